@@ -18,16 +18,16 @@ from ..parts.base import CacheNeed, LayerCache
 from .manager import GroupSpec, PageTable
 
 
-def group_layers(needs: List[CacheNeed]) -> Tuple[List[Tuple[int, int, int, int]], List[int]]:
-    """Group keys (kv_heads, head_dim, window, value width) in order of first use,
+def group_layers(needs: List[CacheNeed]) -> Tuple[List[Tuple[int, int, int, int, bool]], List[int]]:
+    """Group keys (kv_heads, head_dim, window, value width, values inside the keys) in order of first use,
     and for every layer the index of its group (-1: the layer holds no pages)."""
-    keys: List[Tuple[int, int, int, int]] = []
+    keys: List[Tuple[int, int, int, int, bool]] = []
     of_layer: List[int] = []
     for need in needs:
         if need.kind != "kv":
             of_layer.append(-1)
             continue
-        key = (need.kv_heads, need.head_dim, need.window, need.value_dim)
+        key = (need.kv_heads, need.head_dim, need.window, need.value_dim, need.values_in_keys)
         if key not in keys:
             keys.append(key)
         of_layer.append(keys.index(key))
@@ -40,7 +40,8 @@ def bytes_per_page(needs: List[CacheNeed], page_size: int, elem_size: int) -> Li
     out = [0] * len(keys)
     for need, g in zip(needs, of_layer):
         if g >= 0:
-            out[g] += need.kv_heads * page_size * (need.head_dim + need.value_dim) * elem_size
+            width = need.head_dim + (0 if need.values_in_keys else need.value_dim)
+            out[g] += need.kv_heads * page_size * width * elem_size
     return out
 
 
@@ -61,8 +62,9 @@ class CachePools:
                 k_shape = (pages_per_group[g], need.kv_heads, page_size, need.head_dim)
                 v_shape = (pages_per_group[g], need.kv_heads, page_size, need.value_dim)
                 # zeros, not uninitialised memory: rows that a tile loads but masks must be finite
-                self.layers.append(LayerCache(need, g, torch.zeros(k_shape, dtype=dtype, device=device),
-                                              torch.zeros(v_shape, dtype=dtype, device=device), page_size))
+                k_pool = torch.zeros(k_shape, dtype=dtype, device=device)
+                v_pool = k_pool if need.values_in_keys else torch.zeros(v_shape, dtype=dtype, device=device)
+                self.layers.append(LayerCache(need, g, k_pool, v_pool, page_size))
             elif need.kind == "state":
                 st = torch.zeros((max_requests, *need.state_shape), dtype=need.state_dtype,
                                  device=device)
@@ -73,7 +75,7 @@ class CachePools:
     def nbytes(self) -> int:
         n = 0
         for lc in self.layers:
-            for t in (lc.k, lc.v, lc.state):
+            for t in (lc.k, lc.v if lc.v is not lc.k else None, lc.state):
                 if t is not None:
                     n += t.numel() * t.element_size()
         return n

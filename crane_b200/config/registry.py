@@ -3,7 +3,8 @@ the function that lays the model out as a ``ModelSpec``.
 
 Lookup follows the reference's detection order
 (crane-serve/src/engine/model_factory.rs:100-180): an explicit model type,
-then ``architectures`` of config.json, then ``model_type``; names are matched
+then ``architectures`` (or the single name ``architecture``) of config.json,
+then ``model_type``; names are matched
 without regard to case.  Unlike the reference (model_factory.rs:174-178: falls
 back to another model with a warning) an unknown architecture is an error that
 lists what is registered.
@@ -69,7 +70,10 @@ def resolve(config: Dict[str, Any], model_type: Optional[str] = None) -> Archite
             raise UnknownArchitecture(
                 f"model type '{hint}' is not registered; registered: {', '.join(registered())}")
         return arch
-    for a in config.get("architectures") or []:
+    named = list(config.get("architectures") or [])
+    if isinstance(config.get("architecture"), str):
+        named.append(config["architecture"])
+    for a in named:
         tried.append(str(a))
         arch = _lookup(str(a))
         if arch is not None:

@@ -1,6 +1,9 @@
 // Attention over the paged cache on the FP32 cores, for any batch of prompt
-// portions and single decoded tokens and any head size that is a multiple of
-// two up to 256.  One warp per (token, query head): the token at position p of
+// portions and single decoded tokens, any key width up to 1024 and any value
+// width up to 512.  Values are rows of `dv` elements, `v_stride` elements apart,
+// in `v_pool`: a pool of their own, or (v_pool == k_pool, v_stride == d) the
+// leading dv columns of the key rows, which is how latent attention keeps them.
+// One warp per (token, query head): the token at position p of
 // request e attends the keys of positions max(0, p - window + 1) .. p of the
 // same request, found through the request's block table.  Scores, softmax
 // statistics and the weighted sum are float whatever the storage type.
@@ -12,7 +15,8 @@
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int MAXD = 256;
+constexpr int MAXD = 1024;     // widest key row
+constexpr int MAXDV = 512;     // widest value row
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -20,9 +24,10 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
                             const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                             const int* __restrict__ positions, const int* __restrict__ tok_entry,
                             const int* __restrict__ block_table, int max_blocks, int num_pages,
-                            int page_size, int n_tokens, int nq, int nkv, int d, int window,
-                            float scale, int* err) {
-    __shared__ float q_s[WARPS][MAXD];
+                            int page_size, int n_tokens, int nq, int nkv, int d, int dv,
+                            int v_stride, int window, float scale, int* err) {
+    extern __shared__ float q_all[];              // [WARPS][d]
+    float* q_s = q_all + (threadIdx.x >> 5) * d;
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * WARPS + wib;
     if (warp >= (long long)n_tokens * nq) return;
@@ -32,11 +37,11 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
     if (tok_entry[t] < 0) return;                 // a row that pads the step: it attends to nothing
     const int* table = block_table + (long long)tok_entry[t] * max_blocks;
     const T* qp = q + ((long long)t * nq + h) * d;
-    for (int c = lane; c < d; c += 32) q_s[wib][c] = to_f32(qp[c]);
+    for (int c = lane; c < d; c += 32) q_s[c] = to_f32(qp[c]);
     __syncwarp();
 
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    constexpr int NACC = MAXD / 32;
+    constexpr int NACC = MAXDV / 32;
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
@@ -46,16 +51,16 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
     for (int base = lo; base <= pos; base += 32) {
         const int j = base + lane;
         float s = -INFINITY;
-        long long row = -1;                       // element offset of this lane's key/value row
+        long long row = -1;                       // this lane's key/value row in the pools
         if (j <= pos) {
             const int page = table[j / page_size];
             if (page < 0 || page >= num_pages) {
                 bad = true;
             } else {
-                row = (((long long)page * nkv + g) * page_size + j % page_size) * d;
-                const T* kp = k_pool + row;
+                row = ((long long)page * nkv + g) * page_size + j % page_size;
+                const T* kp = k_pool + row * d;
                 float dot = 0.f;
-                for (int c = 0; c < d; ++c) dot = fmaf(q_s[wib][c], to_f32(kp[c]), dot);
+                for (int c = 0; c < d; ++c) dot = fmaf(q_s[c], to_f32(kp[c]), dot);
                 s = dot * scale;
             }
         }
@@ -72,21 +77,21 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long rj = __shfl_sync(0xffffffffu, row, jj);
             if (rj < 0) continue;
-            const T* vp = v_pool + rj;
+            const T* vp = v_pool + rj * v_stride;
 #pragma unroll
             for (int i = 0; i < NACC; ++i) {
                 const int c = lane + 32 * i;
-                if (c < d) acc[i] = fmaf(pj, to_f32(vp[c]), acc[i]);
+                if (c < dv) acc[i] = fmaf(pj, to_f32(vp[c]), acc[i]);
             }
         }
     }
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    T* op = out + ((long long)t * nq + h) * d;
+    T* op = out + ((long long)t * nq + h) * dv;
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
         const int c = lane + 32 * i;
-        if (c < d) op[c] = from_f32<T>(acc[i] * inv);
+        if (c < dv) op[c] = from_f32<T>(acc[i] * inv);
     }
 }
 }  // namespace
@@ -95,21 +100,24 @@ CRANE_API int crane_paged_attention_simt(int dtype, const void* q, void* out, co
                                          const void* v_pool, const int* positions,
                                          const int* tok_entry, const int* block_table,
                                          int max_blocks, int num_pages, int page_size,
-                                         int n_tokens, int nq, int nkv, int d, int window,
-                                         float scale, int* err, cudaStream_t st) {
+                                         int n_tokens, int nq, int nkv, int d, int dv,
+                                         int v_stride, int window, float scale, int* err,
+                                         cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    if (d > MAXD || d <= 0 || nkv <= 0 || nq % nkv != 0) return (int)cudaErrorInvalidValue;
+    if (d > MAXD || d <= 0 || dv > MAXDV || dv <= 0 || v_stride < dv || nkv <= 0 || nq % nkv != 0)
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)WARPS * d * sizeof(float);
     const long long warps = (long long)n_tokens * nq;
     const int blocks = (int)((warps + WARPS - 1) / WARPS);
     if (dtype == 0)
-        paged_attention_simt_kernel<float><<<blocks, WARPS * 32, 0, st>>>(
+        paged_attention_simt_kernel<float><<<blocks, WARPS * 32, smem, st>>>(
             (const float*)q, (float*)out, (const float*)k_pool, (const float*)v_pool, positions,
-            tok_entry, block_table, max_blocks, num_pages, page_size, n_tokens, nq, nkv, d, window,
-            scale, err);
+            tok_entry, block_table, max_blocks, num_pages, page_size, n_tokens, nq, nkv, d, dv,
+            v_stride, window, scale, err);
     else
-        paged_attention_simt_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, st>>>(
+        paged_attention_simt_kernel<__nv_bfloat16><<<blocks, WARPS * 32, smem, st>>>(
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, tok_entry, block_table, max_blocks, num_pages,
-            page_size, n_tokens, nq, nkv, d, window, scale, err);
+            page_size, n_tokens, nq, nkv, d, dv, v_stride, window, scale, err);
     return crane_launch_status();
 }

@@ -15,59 +15,6 @@ int g_crane_pdl = 1;
 
 CRANE_API void crane_set_pdl(int on) { g_crane_pdl = on ? 1 : 0; }
 
-__device__ __forceinline__ float2 ld2(const float* p) { return *(const float2*)p; }
-__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {
-    return __bfloat1622float2(*(const __nv_bfloat162*)p);
-}
-__device__ __forceinline__ void st2(float* p, float a, float b) { *(float2*)p = make_float2(a, b); }
-__device__ __forceinline__ void st2(__nv_bfloat16* p, float a, float b) {
-    *(__nv_bfloat162*)p = __floats2bfloat162_rn(a, b);
-}
-
-// A GEMM result is either one tensor of T or `n_parts` float partial sums
-// (split-K), laid out [part][row][col]; readers add the partials in a fixed
-// order and round once to T, so that both forms give the same value.
-template <typename T>
-struct GemmOut {
-    const T* whole;
-    const float* parts;
-    int n_parts;
-    long long part_stride;
-    // The partial sums are fetched eight at a time (all loads in flight together) and added in
-    // slice order, so the sum is the same as a one-by-one loop's.
-    __device__ __forceinline__ float load(long long idx) const {
-        if (parts == nullptr) return to_f32(whole[idx]);
-        float s = 0.f;
-        for (int i = 0; i < n_parts; i += 8) {
-            float p[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                p[j] = (i + j < n_parts) ? parts[(long long)(i + j) * part_stride + idx] : 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s += p[j];
-        }
-        return to_f32(from_f32<T>(s));
-    }
-    // two neighbours at once; idx even and the tensors' rows evenly long
-    __device__ __forceinline__ float2 load2(long long idx) const {
-        if (parts == nullptr) return ld2(whole + idx);
-        float2 s = make_float2(0.f, 0.f);
-        for (int i = 0; i < n_parts; i += 8) {
-            float2 p[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                p[j] = (i + j < n_parts) ? *(const float2*)(parts + (long long)(i + j) * part_stride + idx)
-                                         : make_float2(0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                s.x += p[j].x;
-                s.y += p[j].y;
-            }
-        }
-        return make_float2(to_f32(from_f32<T>(s.x)), to_f32(from_f32<T>(s.y)));
-    }
-};
-
 // ---------------------------------------------------------------- embedding
 // A token id <= -2 stands for "row (-id - 2) of `deferred`": a token that an
 // earlier launch on this stream sampled and the host has not seen yet.
@@ -701,9 +648,6 @@ static bool norm_cluster_on() {
 
 // ------------------------------------------------------------------ C ABI
 // dtype: 0 = float, 1 = bf16.  Every function returns the CUDA launch status.
-#define DISPATCH_T(dtype, ...)                                   \
-    if ((dtype) == 0) { using T = float; __VA_ARGS__; }          \
-    else { using T = __nv_bfloat16; __VA_ARGS__; }
 
 CRANE_API int crane_embed_gather(int dtype, const int* tokens, const void* table, float* x,
                                  int n_tokens, int hidden, int vocab, const int* deferred,

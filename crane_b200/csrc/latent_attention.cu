@@ -1,0 +1,173 @@
+// Latent attention: keys and values of all heads are up-projections of one cached latent vector
+// c [rank] per position, plus one rotated key part kr [rot] shared by all heads.  With
+// k_h = U_h c and v_h = V_h c the score of head h is q_h . k_h + qr_h . kr = (U_h^T q_h) . c + qr_h . kr
+// and its output V_h (sum_j p_j c_j): attention runs in the latent space as one shared key/value
+// "head" of width rank + rot (value: the leading rank columns of the same rows), between two small
+// per-head products.  The kernels here are those products and the step that fills the cache:
+//
+// latent_prep   per token: c = RMSNorm(first rank columns of the down projection) * w and the rotated
+//               last rot columns go to the token's cache row [rank + rot]; the rotated part of every
+//               query head goes to columns rank.. of the absorbed query [token, head, rank + rot].
+// head_linear   out[t, h, :] = W_h x[t, h, :] for every head (U_h^T on the unrotated query part; V_h on
+//               the attention's latent output, there times sigmoid(gate)), on the FP32 cores.
+//
+// Rotation: interleaved pairs (2i, 2i + 1) of the leading rot_dims elements of the rotated part,
+// (u, v) -> (u cos - v sin, v cos + u sin); the tables hold cos and sin already scaled.
+// All arithmetic in 32-bit; T is the storage type (float or bf16).
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(GemmOut<T> proj, int cols, int q_off, int dkv_off, int heads, int dim, int rot,
+                   int rank, int rot_dims, const float* __restrict__ cos_tab,
+                   const float* __restrict__ sin_tab, int n_positions,
+                   const int* __restrict__ positions, const int* __restrict__ tok_entry,
+                   const int* __restrict__ block_table, int max_blocks, int num_pages, int page_size,
+                   T* __restrict__ pool, const float* __restrict__ norm_w, float eps,
+                   T* __restrict__ q_abs, int* err) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int e = tok_entry[t];
+    if (e < 0) return;                                  // a row that pads the step
+    int pos = positions[t];
+    if (pos < 0 || pos >= n_positions) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
+        pos = 0;
+    }
+    const long long prow = (long long)t * cols;
+    const int half = rot_dims >> 1, pairs = rot >> 1, width = rank + rot;
+    const float* cs = cos_tab + (long long)pos * half;
+    const float* sn = sin_tab + (long long)pos * half;
+    // the rotated part of every query head
+    for (int i = threadIdx.x; i < heads * pairs; i += blockDim.x) {
+        const int h = i / pairs, p = i % pairs;
+        const long long src = prow + q_off + (long long)h * (dim + rot) + dim + 2 * p;
+        float u = proj.load(src), v = proj.load(src + 1);
+        if (p < half) {
+            const float c = cs[p], s = sn[p];
+            const float u2 = u * c - v * s, v2 = v * c + u * s;
+            u = u2;
+            v = v2;
+        }
+        T* dst = q_abs + ((long long)t * heads + h) * width + rank + 2 * p;
+        dst[0] = from_f32<T>(u);
+        dst[1] = from_f32<T>(v);
+    }
+    if (dkv_off < 0) return;                            // the layer reads another layer's cache
+    const int page = block_table[(long long)e * max_blocks + pos / page_size];
+    const bool ok = page >= 0 && page < num_pages;
+    if (!ok && threadIdx.x == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
+    T* crow = pool + ((long long)(ok ? page : 0) * page_size + pos % page_size) * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        const float v = proj.load(prow + dkv_off + c);
+        ss += v * v;
+    }
+    const float rstd = 1.f / sqrtf(block_sum(ss, scratch) / (float)rank + eps);
+    if (!ok) return;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x)
+        crow[c] = from_f32<T>(proj.load(prow + dkv_off + c) * rstd * norm_w[c]);
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const long long src = prow + dkv_off + rank + 2 * p;
+        float u = proj.load(src), v = proj.load(src + 1);
+        if (p < half) {
+            const float c = cs[p], s = sn[p];
+            const float u2 = u * c - v * s, v2 = v * c + u * s;
+            u = u2;
+            v = v2;
+        }
+        crow[rank + 2 * p] = from_f32<T>(u);
+        crow[rank + 2 * p + 1] = from_f32<T>(v);
+    }
+}
+
+// out[t, h, o] = sum_i w[h][i][o] * x[t, x_off + h * x_head + i]  (i in order 0 .. n_in - 1), then
+// times sigmoid(gate[t, g_off + h * n_out + o]) if a gate is given.  x and gate are columns of
+// one product's result (row pitch x_cols / g_cols).  A CTA takes TT tokens of one head.
+constexpr int HL_TT = 16;
+constexpr int HL_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(HL_THREADS)
+head_linear_kernel(GemmOut<T> x, int x_cols, int x_off, int x_head, const T* __restrict__ w, int n_in,
+                   int n_out, GemmOut<T> gate, int has_gate, int g_cols, int g_off,
+                   const int* __restrict__ tok_entry, T* __restrict__ out, int out_pitch,
+                   int out_head, int n_tokens, int heads) {
+    extern __shared__ float xs[];                       // [HL_TT][n_in]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y, t0 = blockIdx.x * HL_TT;
+    const int nt = min(HL_TT, n_tokens - t0);
+    for (int i = threadIdx.x; i < nt * n_in; i += blockDim.x) {
+        const int tt = i / n_in, c = i % n_in;
+        xs[tt * n_in + c] = x.load((long long)(t0 + tt) * x_cols + x_off + (long long)h * x_head + c);
+    }
+    __syncthreads();
+    const T* wh = w + (long long)h * n_in * n_out;
+    for (int o = threadIdx.x; o < n_out; o += blockDim.x) {
+        float acc[HL_TT];
+#pragma unroll
+        for (int tt = 0; tt < HL_TT; ++tt) acc[tt] = 0.f;
+        for (int i = 0; i < n_in; ++i) {
+            const float wv = to_f32(wh[(long long)i * n_out + o]);
+#pragma unroll
+            for (int tt = 0; tt < HL_TT; ++tt) acc[tt] = fmaf(wv, xs[tt * n_in + i], acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < HL_TT; ++tt) {
+            if (tt >= nt) break;
+            const int t = t0 + tt;
+            if (tok_entry != nullptr && tok_entry[t] < 0) continue;
+            float v = to_f32(from_f32<T>(acc[tt]));
+            if (has_gate) {
+                const float g = gate.load((long long)t * g_cols + g_off + (long long)h * n_out + o);
+                v *= 1.f / (1.f + expf(-g));
+            }
+            out[(long long)t * out_pitch + (long long)h * out_head + o] = from_f32<T>(v);
+        }
+    }
+}
+
+}  // namespace
+
+CRANE_API int crane_latent_prep(int dtype, const void* proj, const float* proj_parts, int n_parts,
+                                long long part_stride, int cols, int q_off, int dkv_off, int heads,
+                                int dim, int rot, int rank, int rot_dims, const float* cos_tab,
+                                const float* sin_tab, int n_positions, const int* positions,
+                                const int* tok_entry, const int* block_table, int max_blocks,
+                                int num_pages, int page_size, void* pool, const float* norm_w, float eps,
+                                void* q_abs, int n_tokens, int* err, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if ((rot & 1) || (rot_dims & 1) || rot_dims > rot || rot_dims < 0) return (int)cudaErrorInvalidValue;
+    DISPATCH_T(dtype, {
+        GemmOut<T> p{(const T*)proj, proj_parts, n_parts, part_stride};
+        return crane_launch(latent_prep_kernel<T>, dim3(n_tokens), dim3(128), 0, st, p, cols, q_off, dkv_off,
+                            heads, dim, rot, rank, rot_dims, cos_tab, sin_tab, n_positions, positions,
+                            tok_entry, block_table, max_blocks, num_pages, page_size, (T*)pool, norm_w, eps,
+                            (T*)q_abs, err);
+    });
+}
+
+CRANE_API int crane_head_linear(int dtype, const void* x, const float* x_parts, int x_n, long long x_stride,
+                                int x_cols, int x_off, int x_head, const void* w, int n_in, int n_out,
+                                const void* gate, const float* g_parts, int g_n, long long g_stride,
+                                int g_cols, int g_off, const int* tok_entry, void* out, int out_pitch,
+                                int out_head, int n_tokens, int heads, cudaStream_t st) {
+    if (n_tokens <= 0 || heads <= 0) return 0;
+    const size_t smem = (size_t)HL_TT * n_in * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    const int has_gate = (gate != nullptr || g_parts != nullptr) ? 1 : 0;
+    DISPATCH_T(dtype, {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(head_linear_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        GemmOut<T> gx{(const T*)x, x_parts, x_n, x_stride};
+        GemmOut<T> gg{(const T*)gate, g_parts, g_n, g_stride};
+        return crane_launch(head_linear_kernel<T>, dim3((n_tokens + HL_TT - 1) / HL_TT, heads),
+                            dim3(HL_THREADS), smem, st, gx, x_cols, x_off, x_head, (const T*)w, n_in, n_out, gg,
+                            has_gate, g_cols, g_off, tok_entry, (T*)out, out_pitch, out_head, n_tokens, heads);
+    });
+}

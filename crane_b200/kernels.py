@@ -28,7 +28,7 @@ _SIGNATURES = {
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
     "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, I, L, I, P, L, P, P],
     "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
-    "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
+    "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_paged_prefill_attention_supports": [I, I, I],
@@ -37,6 +37,11 @@ _SIGNATURES = {
                                            I, I, I, I, I, I, I, I, F, I, I, I, I, F, P, P],
     "crane_prefill_attention_tc_supports": [I, I, I, I],
     "crane_prefill_attention_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
+    "crane_embed_bigram": [I, P, P, P, P, I, I, I, I, L, L, P, P, P, P, P, I, P, I, P, P],
+    "crane_combine_layernorm": [I, P, P, L, I, P, P, I, L, P, P, I, L, P, P, P, P, P, P, P, P, I, I, F, P],
+    "crane_xielu": [I, P, P, I, L, P, L, P, P],
+    "crane_latent_prep": [I, P, P, I, L, I, I, I, I, I, I, I, I, P, P, I, P, P, P, I, I, I, P, P, F, P, I, P, P],
+    "crane_head_linear": [I, P, P, I, L, I, I, I, P, I, I, P, P, I, L, I, I, P, P, I, I, I, I, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -187,6 +192,66 @@ class Kernels:
     def to_float(self, t, out) -> None:
         self._check(self.lib.crane_to_float(_dt(t.dtype), t.data_ptr(), out.data_ptr(), t.numel(),
                                             self._stream(t)), "to_float")
+
+    # ---- parts of other layer designs ------------------------------------
+    def embed_bigram(self, tokens, table, bigram, x, buckets, mul_prev, mul_cur, positions, tok_entry,
+                     cu_q, slots, last_token, err, deferred=None) -> None:
+        """x[t] = table[token] + bigram[(previous * mul_prev + token * mul_cur) mod buckets];
+        a sequence's first token takes row ``buckets``.  ``last_token`` int32 [slots]: the
+        token before each request's next one, read and replaced here.  ``bigram`` None:
+        the plain embedding."""
+        n, hidden = x.shape
+        self._check(self.lib.crane_embed_bigram(
+            _dt(table.dtype), tokens.data_ptr(), table.data_ptr(), _ptr(bigram), x.data_ptr(), n, hidden,
+            table.shape[0], int(buckets), int(mul_prev), int(mul_cur), positions.data_ptr(),
+            tok_entry.data_ptr(), cu_q.data_ptr(), slots.data_ptr(), last_token.data_ptr(),
+            last_token.numel(), _ptr(deferred), deferred.numel() if deferred is not None else 0,
+            err.data_ptr(), self._stream(x)), "embed_bigram")
+
+    def combine_layernorm(self, x, hist, n_hist, a: Optional[Act], f: Optional[Act], dwa, rows,
+                          w1, b1, out1, w2, b2, out2, eps: float) -> None:
+        """X = x + (a + f); hist[n_hist - 1] = X; x = sum_j dwa[j] hist[j] (``dwa`` None: x = X);
+        out1 / out2 = the layer norms (w1, b1) / (w2, b2) of the new x.  ``hist`` float
+        [slots, rows, hidden] or None.  With ``rows`` only those rows are read and
+        nothing but out1 / out2 is written."""
+        aw, ap, an, astr = (None, None, 0, 0) if a is None else _split(a)
+        fw, fp, fn, fstr = (None, None, 0, 0) if f is None else _split(f)
+        n_rows = out1.shape[0]
+        self._check(self.lib.crane_combine_layernorm(
+            _dt(out1.dtype), x.data_ptr(), _ptr(hist), hist.stride(0) if hist is not None else 0,
+            int(n_hist), aw, ap, an, astr, fw, fp, fn, fstr, _ptr(dwa), _ptr(rows), w1.data_ptr(),
+            b1.data_ptr(), out1.data_ptr(), _ptr(w2), _ptr(b2), _ptr(out2), n_rows, x.shape[1],
+            float(eps), self._stream(x)), "combine_layernorm")
+
+    def xielu(self, up: Act, out, pq) -> None:
+        """out = xIELU(up) with the two float numbers ``pq`` (p, q) on the device."""
+        whole, parts, n_parts, stride = _split(up)
+        self._check(self.lib.crane_xielu(_dt(out.dtype), whole, parts, n_parts, stride, out.data_ptr(),
+                                         out.numel(), pq.data_ptr(), self._stream(out)), "xielu")
+
+    def latent_prep(self, proj: Act, cols, q_off, dkv_off, heads, dim, rot, rank, rot_dims, cos, sin,
+                    positions, tok_entry, block_table, pool, page_size, norm_w, eps, q_abs, err) -> None:
+        """Latent attention's cache write and query rotation; ``dkv_off`` < 0: the
+        layer writes no cache.  ``pool`` [pages, 1, page_size, rank + rot]."""
+        whole, parts, n_parts, stride = _split(proj)
+        self._check(self.lib.crane_latent_prep(
+            _dt(q_abs.dtype), whole, parts, n_parts, stride, int(cols), int(q_off), int(dkv_off), heads, dim,
+            rot, rank, rot_dims, cos.data_ptr(), sin.data_ptr(), cos.shape[0], positions.data_ptr(),
+            tok_entry.data_ptr(), block_table.data_ptr(), block_table.shape[1], pool.shape[0], page_size,
+            pool.data_ptr(), _ptr(norm_w), float(eps), q_abs.data_ptr(), q_abs.shape[0], err.data_ptr(),
+            self._stream(q_abs)), "latent_prep")
+
+    def head_linear(self, x: Act, x_cols, x_off, x_head, w, n_in, n_out, out, out_pitch, out_head,
+                    heads, tok_entry=None, gate: Optional[Act] = None, g_cols=0, g_off=0) -> None:
+        """out[t, h, :n_out] = w[h] (as [n_in, n_out]) applied to x[t, x_off + h * x_head : + n_in],
+        times sigmoid(gate[t, g_off + h * n_out : ...]) if a gate is given."""
+        xw, xp, xn, xs = _split(x)
+        gw, gp, gn, gs = (None, None, 0, 0) if gate is None else _split(gate)
+        n_tokens = out.shape[0]
+        self._check(self.lib.crane_head_linear(
+            _dt(out.dtype), xw, xp, xn, xs, int(x_cols), int(x_off), int(x_head), w.data_ptr(), int(n_in),
+            int(n_out), gw, gp, gn, gs, int(g_cols), int(g_off), _ptr(tok_entry), out.data_ptr(),
+            int(out_pitch), int(out_head), n_tokens, int(heads), self._stream(out)), "head_linear")
 
     # ---- matrix product on the FP32 cores ------------------------------
     def gemm_simt(self, a, w, bias, out) -> None:
@@ -370,12 +435,17 @@ class Kernels:
 
     # ---- attention ------------------------------------------------------
     def paged_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table,
-                             page_size, nq, nkv, d, window, scale, err) -> None:
+                             page_size, nq, nkv, d, window, scale, err, dv=None, v_stride=None) -> None:
+        """``dv``: width of a value row (default: the keys'), ``v_stride``: elements
+        between value rows (default ``dv``).  With ``v_pool`` the key pool itself and
+        ``v_stride == d`` the values are the leading ``dv`` columns of the key rows."""
+        dv = d if dv is None else int(dv)
+        v_stride = dv if v_stride is None else int(v_stride)
         self._check(self.lib.crane_paged_attention_simt(
             _dt(q.dtype), q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
             positions.data_ptr(), tok_entry.data_ptr(), block_table.data_ptr(),
-            block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, int(window),
-            float(scale), err.data_ptr(), self._stream(q)), "paged_attention_simt")
+            block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, dv, v_stride,
+            int(window), float(scale), err.data_ptr(), self._stream(q)), "paged_attention_simt")
 
     @staticmethod
     def decode_splits(entries: int, nkv: int, sms: int, cap: int = 64, max_keys: int = 1 << 30) -> int:

@@ -73,6 +73,8 @@ class CacheNeed:
     all positions (``window == 0``) or the last ``window``.  The two pools are
     shaped independently, so values wider or narrower than keys need no change
     to the cache.
+    ``values_in_keys``: the values are the leading ``v_head_dim`` columns of the key
+    rows (latent attention): there is no V pool, ``LayerCache.v`` is the K pool.
     ``kind == "state"``: one tensor of ``state_shape`` / ``state_dtype`` in the
     request's slot.  ``kind == "none"``: nothing (or another layer's cache)."""
     kind: str = "none"
@@ -82,6 +84,7 @@ class CacheNeed:
     state_shape: Tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
     v_head_dim: int = 0
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:

@@ -54,3 +54,52 @@ class LMHead(Part):
     def forward(self, h, rt):
         # wanted rows are few when serving; the buffer grows if a caller wants more
         return rt.linear(h, self.weight, None, "logits", out_dtype=torch.float32, cap=64)
+
+
+@register_part("embed", "bigram_embedding")
+class BigramEmbedding(Part):
+    """x0 = E[token] + B[(previous * mul_prev + token * mul_cur) mod buckets]; a sequence's
+    first token takes B's last row (number ``buckets``).  params: ``vocab_size``,
+    ``hidden_size``, ``table`` (tensor name), ``bigram``: None or ``{table, buckets, mul_prev,
+    mul_cur}``.  Tensors: E [V,H], B [buckets + 1, H].
+
+    The token before a portion's first one is the request's state: one int32 in the
+    request's slot, kept by the cache manager like a mixer's state, read and replaced on
+    the device by the embedding kernel (the token may be one that the host has not seen
+    yet).  The kernel leaves rows of no entry and entries without rows alone, so steps
+    padded for graph replay are safe."""
+    kind = "embed"
+    needs_context = True
+    state_graph_safe = True
+
+    @classmethod
+    def manifest(cls, spec):
+        a = spec.params
+        m = {spec.prefix + a["table"]: TensorSpec((a["vocab_size"], a["hidden_size"]))}
+        if a.get("bigram"):
+            m[spec.prefix + a["bigram"]["table"]] = TensorSpec((a["bigram"]["buckets"] + 1, a["hidden_size"]))
+        return m
+
+    def load(self, weights, rt):
+        a = self.params
+        self.table = weights[self.prefix + a["table"]]
+        bg = a.get("bigram")
+        self.bigram = weights[self.prefix + bg["table"]] if bg else None
+        self.buckets, self.mul_prev, self.mul_cur = ((int(bg["buckets"]), int(bg["mul_prev"]), int(bg["mul_cur"]))
+                                                     if bg else (0, 0, 0))
+
+    def cache_need(self):
+        from .base import CacheNeed
+        if self.bigram is None:
+            return CacheNeed("none")
+        return CacheNeed("state", state_shape=(1,), state_dtype=torch.int32)
+
+    def forward(self, tokens, x, rt, deferred=None, ctx=None, cache=None):
+        state = cache.state if cache is not None and cache.state is not None else None
+        if self.bigram is None or state is None:
+            rt.kernels.embed_gather(tokens, self.table, x, rt.err, deferred)
+        else:
+            rt.kernels.embed_bigram(tokens, self.table, self.bigram, x, self.buckets, self.mul_prev,
+                                    self.mul_cur, ctx.positions, ctx.tok_entry, ctx.cu_q, ctx.slots, state,
+                                    rt.err, deferred)
+        rt.launches += 1

@@ -50,3 +50,30 @@ class SwiGLU(Part):
         rt.kernels.silu_mul(gu, act, self.blocked)
         rt.launches += 1
         return rt.linear(act, self.down, None, "ffn_down")
+
+
+@register_part("ffn", "xielu_mlp")
+class XieluMlp(Part):
+    """down(act(up(h))), no biases, act = xIELU with two learnt numbers (p, q):
+    z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2, in 32-bit.
+    params: ``hidden_size``, ``intermediate_size``.  Tensors: ``<prefix>up`` [I,H],
+    ``<prefix>down`` [H,I], ``<prefix>act`` [2] (kept float)."""
+    kind = "ffn"
+
+    @classmethod
+    def manifest(cls, spec):
+        h, i = spec.params["hidden_size"], spec.params["intermediate_size"]
+        p = spec.prefix
+        return {p + "up": TensorSpec((i, h)), p + "down": TensorSpec((h, i)), p + "act": TensorSpec((2,), "float32", "unit")}
+
+    def load(self, weights, rt):
+        p = self.prefix
+        self.inter = int(self.params["intermediate_size"])
+        self.up, self.down, self.pq = weights[p + "up"], weights[p + "down"], weights[p + "act"]
+
+    def forward(self, h, ctx, rt):
+        up = rt.linear(h, self.up, None, "ffn_up")
+        act = rt.ws.get("ffn_act", h.shape[0], self.inter, rt.dtype)
+        rt.kernels.xielu(up, act, self.pq)
+        rt.launches += 1
+        return rt.linear(act, self.down, None, "ffn_down")

@@ -62,8 +62,13 @@ class DecoderModel:
     def cache_needs(self) -> List[CacheNeed]:
         """Per step of the schedule, what its mixer keeps between engine steps
         (nothing for a step that reads another step's cache)."""
-        return [self.blocks[s.layer].mixer.cache_need() if s.cache_of is None else CacheNeed("none")
-                for s in self.spec.schedule]
+        needs = [self.blocks[s.layer].mixer.cache_need() if s.cache_of is None else CacheNeed("none")
+                 for s in self.spec.schedule]
+        # an embedding that keeps something per request (the token before the next one) gets the
+        # place behind the schedule's
+        if hasattr(self.embed, "cache_need"):
+            needs.append(self.embed.cache_need())
+        return needs
 
     def capturable(self) -> bool:
         """Whether every part says that its forward can be recorded in a CUDA graph."""
@@ -74,8 +79,8 @@ class DecoderModel:
 
     def state_graph_safe(self) -> bool:
         """Whether every mixer that keeps per-request state bears graphs and padding."""
-        return all(getattr(b.mixer, "state_graph_safe", False) for b in self.blocks
-                   if b.mixer.cache_need().kind == "state")
+        keepers = [b.mixer for b in self.blocks] + ([self.embed] if hasattr(self.embed, "cache_need") else [])
+        return all(getattr(p, "state_graph_safe", False) for p in keepers if p.cache_need().kind == "state")
 
     def forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
         """Runs the step's tokens through the schedule (``caches``: one entry
@@ -95,7 +100,11 @@ class DecoderModel:
         rt.begin_step()
         n = ctx.n_tokens
         x = rt.ws.get("residual", n, self.spec.hidden_size, torch.float32)
-        self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None))
+        if getattr(self.embed, "needs_context", False):
+            self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None), ctx=ctx,
+                               cache=caches[len(self.spec.schedule)])
+        else:
+            self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None))
         pending = None
         for place, step in enumerate(self.spec.schedule):
             pending = self.blocks[step.layer].forward(x, pending, ctx, caches[step.cache_step(place)], rt)

@@ -33,3 +33,70 @@ class RMSNorm(Part):
         rt.kernels.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
         rt.launches += 1
         return out
+
+
+class BranchSum:
+    """What a parallel block hands on instead of adding it: the outputs of its two
+    branches (either may be None) and the part that mixes the sum into the stream
+    (``combine``: a ``depth_average`` part, or None for a plain residual addition).
+    The norm that reads the stream next does the additions in its own kernel."""
+
+    def __init__(self, a, f, combine=None):
+        self.a, self.f, self.combine = a, f, combine
+
+
+def combine_and_norm(x, pending, norm_a, norm_b, rt, rows=None, names=("normed", "normed2")):
+    """Adds what is pending to the float stream ``x`` (a ``BranchSum``, a plain
+    product result or None), lets a ``BranchSum``'s ``combine`` part mix the
+    new layer result with the earlier ones, and returns LayerNorm_a and
+    (``norm_b`` given) LayerNorm_b of the new stream: one kernel.  ``rows``: only
+    x[rows] is read and nothing of the stream is written."""
+    n = x.shape[0] if rows is None else rows.shape[0]
+    out_a = rt.ws.get(names[0], n, norm_a.size, rt.dtype)
+    out_b = rt.ws.get(names[1], n, norm_b.size, rt.dtype) if norm_b is not None else None
+    a = f = combine = None
+    if isinstance(pending, BranchSum):
+        a, f, combine = pending.a, pending.f, pending.combine
+    else:
+        a = pending
+    hist, n_hist, dwa = None, 1, None
+    if combine is not None:
+        hist, n_hist, dwa = combine.history(rt, x.shape[0]), combine.index + 2, combine.weights
+    elif norm_a.history_of is not None and pending is None:
+        # the stream as the embedding leaves it is the first entry of the layers' history
+        hist = norm_a.history_of.history(rt, x.shape[0])
+    rt.kernels.combine_layernorm(x, hist, n_hist, a, f, dwa, rows, norm_a.weight, norm_a.bias, out_a,
+                                 norm_b.weight if norm_b is not None else None,
+                                 norm_b.bias if norm_b is not None else None, out_b, norm_a.eps)
+    rt.launches += 1
+    return out_a, out_b
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(Part):
+    """y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared deviations,
+    all in 32-bit, fused with the additions that precede it.  params: ``size``, ``eps``,
+    ``weight`` / ``bias`` (tensor names behind the prefix; default "weight" / "bias").
+    Both tensors [size], kept float."""
+    kind = "norm"
+    history_of = None        # set by a block whose layer results are kept: its ``depth_average`` part
+
+    @classmethod
+    def _names(cls, spec):
+        return (spec.prefix + spec.params.get("weight", "weight"), spec.prefix + spec.params.get("bias", "bias"))
+
+    @classmethod
+    def manifest(cls, spec):
+        w, b = cls._names(spec)
+        size = (spec.params["size"],)
+        return {w: TensorSpec(size, "float32", "scale"), b: TensorSpec(size, "float32", "offset")}
+
+    def load(self, weights, rt):
+        w, b = self._names(self.spec)
+        self.weight, self.bias = weights[w], weights[b]
+        self.eps = float(self.params["eps"])
+        self.size = int(self.params["size"])
+
+    def forward(self, x, delta, rt, rows=None, name="normed"):
+        """As ``RMSNorm.forward``; ``delta`` may also be a ``BranchSum``."""
+        return combine_and_norm(x, delta, self, None, rt, rows, (name, name + "2"))[0]

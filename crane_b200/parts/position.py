@@ -51,3 +51,50 @@ class Rope(Part):
             sin = np.sin(angles.astype(np.float64)).astype(np.float32)
             _TABLES[key] = (torch.from_numpy(cos).to(rt.device), torch.from_numpy(sin).to(rt.device))
         return _TABLES[key]
+
+
+@register_part("position", "yarn_rope")
+class YarnRope(Part):
+    """Rotary angles a = p * f_i over ``dims`` rotated elements, f_i = base^(-2i/dims), with YaRN
+    scaling (``scaling``: factor, original, fast, slow; or None):
+    dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0),
+    hi = min(ceil(dim(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    f_i <- f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin times 0.1 ln(factor) + 1.
+    params: ``dims``, ``base``, ``scaling``, ``max_positions``.  No tensors.  ``tables(rt, limit)``
+    gives (cos, sin) [positions < limit, dims / 2] in float, the factor folded in; the angles are
+    formed in 64-bit on the host and rounded once."""
+    kind = "position"
+
+    def width(self) -> int:
+        return int(self.params["dims"])
+
+    def frequencies(self):
+        dims, base = self.width(), float(self.params["base"])
+        i = np.arange(dims // 2, dtype=np.float64)
+        f = base ** (-2.0 * i / dims) if dims else i
+        sc = self.params.get("scaling")
+        mult = 1.0
+        if sc and dims:
+            def dim_of(t):
+                return dims * np.log(float(sc["original"]) / (2.0 * np.pi * float(t))) / (2.0 * np.log(base))
+            lo = max(int(np.floor(dim_of(sc["fast"]))), 0)
+            hi = min(int(np.ceil(dim_of(sc["slow"]))), dims - 1)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / float(sc["factor"]) * ramp + f * (1.0 - ramp)
+            mult = 0.1 * float(np.log(float(sc["factor"]))) + 1.0
+        return f, mult
+
+    def tables(self, rt, limit: int):
+        n = min(int(self.params["max_positions"]), int(limit))
+        sc = self.params.get("scaling") or {}
+        key = ("yarn", self.width(), float(self.params["base"]),
+               tuple(sorted((k, float(v)) for k, v in sc.items())), n, str(rt.device))
+        if key not in _TABLES:
+            f, mult = self.frequencies()
+            angles = np.arange(n, dtype=np.float64)[:, None] * f[None, :]
+            cos = (np.cos(angles) * mult).astype(np.float32).reshape(n, -1)
+            sin = (np.sin(angles) * mult).astype(np.float32).reshape(n, -1)
+            if cos.shape[1] == 0:           # nothing is rotated: a column that no kernel reads
+                cos, sin = np.ones((n, 1), np.float32), np.zeros((n, 1), np.float32)
+            _TABLES[key] = (torch.from_numpy(cos).to(rt.device), torch.from_numpy(sin).to(rt.device))
+        return _TABLES[key]

@@ -96,11 +96,14 @@ class Runtime:
     # ---- matrix product -------------------------------------------------
     def linear(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], name: str,
                out_dtype: Optional[torch.dtype] = None, cap: Optional[int] = None,
-               hint_next: bool = True) -> Act:
+               hint_next: bool = True, hold: bool = False) -> Act:
         """x[M,K] @ w[N,K]^T (+ bias[N], float) -> [M,N] in ``out_dtype`` (the
         model dtype unless stated).  ``hint_next`` False: this product does not
         ask for the next product's weights (its caller streams so much between
-        the two that they would not stay in L2)."""
+        the two that they would not stay in L2).  ``hold``: the result is read
+        only after other products have run (a branch of a parallel block): if it
+        is left as partial sums, they get a buffer of this product's own name
+        instead of the one that all products of its width share."""
         M, K = x.shape
         N = w.shape[0]
         out_dtype = out_dtype or self.dtype
@@ -109,7 +112,7 @@ class Runtime:
             self.kernels.gemm_simt(x, w, bias, out)
             self.launches += 1
             return out
-        return self._linear_bf16(x, w, bias, out, hint_next)
+        return self._linear_bf16(x, w, bias, out, hint_next, name if hold else None)
 
     def linear_silu_mul(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
         """out[M, N/2] = silu(gate) * up of x @ w^T in one kernel, for w whose rows
@@ -129,10 +132,11 @@ class Runtime:
         self.launches += 1
         return True
 
-    def _linear_bf16(self, x, w, bias, out, hint_next: bool = True) -> Act:
+    def _linear_bf16(self, x, w, bias, out, hint_next: bool = True, own_parts: Optional[str] = None) -> Act:
         k = self.kernels
         M, K = x.shape
         N = w.shape[0]
+        tag = str(N) if own_parts is None else str(N) + ":" + own_parts
         if self.use_tcgen05 and k.tcgen05_takes(x, w):
             if M <= self.split_rows:
                 # few tokens: the weight rows fill the MMA's 128-wide side (the tokens its 16 to
@@ -150,7 +154,7 @@ class Runtime:
                 if not hint_next or M != 1:
                     nxt = None
                 if slices > 1:
-                    parts = self.ws.get("splitk:" + str(N), slices * self.split_rows, N,
+                    parts = self.ws.get("splitk:" + tag, slices * self.split_rows, N,
                                         torch.float32, cap=slices * self.split_rows)
                     parts = parts[:slices * M].view(slices, M, N)
                     k.gemm_tcgen05(x, w, bias, parts, self.err, split_k=slices, swap=True, bn=bn, prefetch=nxt)
@@ -173,7 +177,7 @@ class Runtime:
                     slices = min(self.num_sms // tiles, 4)
                     if slices >= 2 and K // slices >= 1536:
                         # at most 4 slices of 4 * split_rows tokens: the buffer never has to grow
-                        parts = self.ws.get("splitk_wide:" + str(N), slices * M, N, torch.float32,
+                        parts = self.ws.get("splitk_wide:" + tag, slices * M, N, torch.float32,
                                             cap=16 * self.split_rows).view(slices, M, N)
                         k.gemm_tcgen05(x, w, bias, parts, self.err, split_k=slices, swap=True, bn=256)
                         self.launches += 1

@@ -45,6 +45,10 @@ class WeightsError(ValueError):
 class TensorSpec:
     shape: Tuple[int, ...]
     keep: str = "model"        # "model" | "float32" | "keep"
+    # how random weights are drawn for it, where the name and ``keep`` do not say: "" (by name),
+    # "scale" (1 + noise: a norm's weight), "offset" (noise: a bias), "mix" (weights of an average
+    # over the tensor's length), "unit" (numbers of order one)
+    init: str = ""
 
 
 def _target_dtype(spec: TensorSpec, stored: torch.dtype, model_dtype: torch.dtype) -> torch.dtype:
