@@ -42,6 +42,8 @@ _SIGNATURES = {
     "crane_xielu": [I, P, P, I, L, P, L, P, P],
     "crane_latent_prep": [I, P, P, I, L, I, I, I, I, I, I, I, I, P, P, I, P, P, P, I, I, I, P, P, F, P, I, P, P],
     "crane_head_linear": [I, P, P, I, L, I, I, I, P, I, I, P, P, I, L, I, I, P, P, I, I, I, I, P],
+    "crane_latent_attention_mma_supports": [I, I],
+    "crane_latent_attention_mma": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -252,6 +254,22 @@ class Kernels:
             _dt(out.dtype), xw, xp, xn, xs, int(x_cols), int(x_off), int(x_head), w.data_ptr(), int(n_in),
             int(n_out), gw, gp, gn, gs, int(g_cols), int(g_off), _ptr(tok_entry), out.data_ptr(),
             int(out_pitch), int(out_head), n_tokens, int(heads), self._stream(out)), "head_linear")
+
+    def latent_attention_mma_supports(self, dk: int, dv: int) -> bool:
+        return bool(self.lib.crane_latent_attention_mma_supports(int(dk), int(dv)))
+
+    def latent_attention_mma(self, q, out, pool, cu_q, kv_len, block_table, page_size, tiles, splits,
+                             small: bool, heads, dk, dv, scale, part_o, part_ml, err) -> None:
+        """Attention over cache rows [dk] whose values are their leading ``dv`` columns,
+        ``heads`` query heads per token (bfloat16).  One launch takes the entries of at
+        most 16 rows (tokens x heads) in tiles of 16 (``small``) or the others in tiles
+        of 64; ``tiles``: at least how many there are.  ``splits`` > 1 cuts every tile's
+        keys into slices that a second kernel merges (scratch: ``part_o``, ``part_ml``)."""
+        self._check(self.lib.crane_latent_attention_mma(
+            q.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml), pool.data_ptr(), cu_q.data_ptr(),
+            kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], pool.shape[0], page_size,
+            kv_len.shape[0], int(tiles), int(splits), 1 if small else 0, heads, dk, dv, float(scale),
+            err.data_ptr(), self._stream(q)), "latent_attention_mma")
 
     # ---- matrix product on the FP32 cores ------------------------------
     def gemm_simt(self, a, w, bias, out) -> None:

@@ -117,14 +117,64 @@ class LatentAttention(Part):
         k.head_linear(proj, self.cols, 0, dim + rot, self.uk, dim, r, q_abs, H * width, width, H,
                       tok_entry=ctx.tok_entry)
         o_lat = rt.ws.get("latent_o", n, H * r, rt.dtype)
-        k.paged_attention_simt(q_abs, o_lat, cache.k, cache.k, ctx.positions, ctx.tok_entry, table,
-                               cache.page_size, H, 1, width, 0, self.scale, rt.err, dv=r, v_stride=width)
+        shape_only = ctx.graph_key is not None or ctx.graph_bucket > 0
+        rt.launches += latent_attention_kernel(
+            k, q_abs, o_lat, cache.k, ctx.positions, ctx.tok_entry, ctx.cu_q, ctx.kv_len, ctx.h_cu_q,
+            ctx.h_kv_len, table, cache.page_size, H, r, rot, self.scale, rt.err, rt.exact,
+            padded=ctx.n_tokens if shape_only else None, num_sms=rt.num_sms,
+            scratch=lambda name, rows, cols, cap: rt.ws.get(name, rows, cols, torch.float32, cap=cap),
+            max_small=rt.max_decode_rows)
         o = rt.ws.get("attn_o", n, H * vd, rt.dtype)
         k.head_linear(o_lat, H * r, 0, r, self.uv_t, r, vd, o, H * vd, vd, H, tok_entry=ctx.tok_entry,
                       gate=proj if self.gated else None, g_cols=self.cols, g_off=self.g_off)
-        rt.launches += 4
+        rt.launches += 3
         # (hold: a parallel block adds this only after its feed-forward's products have run)
         return rt.linear(o, self.o_w, None, "attn_out", hold=True)
+
+
+def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len, h_cu_q, h_kv_len, table,
+                            page_size, heads, rank, rot, scale, err, exact, padded=None, num_sms=148,
+                            scratch=None, max_small=64) -> int:
+    """out [N, heads * rank] = attention of q [N, heads * (rank + rot)] over the cache rows of
+    ``pool`` [pages, 1, page_size, rank + rot], whose values are their leading ``rank`` columns.
+    True 32-bit, or widths that the tensor-core kernel does not take: the FP32-core kernel.
+    Else the tensor-core kernel, once for the entries of at most 16 rows (decoded tokens) and
+    once for the others, each with its keys in as many slices as fill the device.
+    ``padded``: the step's shape is fixed by a captured graph (this many rows): tile counts
+    and slices are then bounds that depend on the shape alone.  Returns the launches."""
+    width = rank + rot
+    if exact or not k.latent_attention_mma_supports(width, rank):
+        k.paged_attention_simt(q, out, pool, pool, positions, tok_entry, table, page_size, heads, 1, width, 0,
+                               scale, err, dv=rank, v_stride=width)
+        return 1
+    n_entries = kv_len.shape[0]
+    if padded is not None:
+        small_tiles = n_entries if heads <= 16 else 0
+        big_tiles = n_entries + (int(padded) * heads) // 64
+        most_keys = 1 << 30
+    else:
+        rows = (h_cu_q[1:n_entries + 1] - h_cu_q[:n_entries]) * heads
+        small_tiles = int(((rows > 0) & (rows <= 16)).sum())
+        big_tiles = int(((rows[rows > 16] + 63) // 64).sum())
+        most_keys = int(h_kv_len[:n_entries].max())
+    if scratch is None:
+        scratch = lambda name, n, cols, cap: torch.empty((n, cols), dtype=torch.float32, device=q.device)
+    launches = 0
+    for small, tiles in ((True, small_tiles), (False, big_tiles)):
+        if tiles == 0:
+            continue
+        bm = 16 if small else 64
+        # slices: enough CTAs to fill the device (twice over for the one-warp tiles), none of fewer than 128 keys
+        splits = max(1, min(16 if small else 8, ((2 if small else 1) * num_sms) // tiles, -(-most_keys // 128)))
+        part_o = part_ml = None
+        if splits > 1:
+            cap = (max_small * 16 * 16) if small else (num_sms + 1) * 64
+            part_o = scratch("latent_part_o" + ("_s" if small else ""), tiles * splits * bm, rank, max(cap, tiles * splits * bm))
+            part_ml = scratch("latent_part_ml" + ("_s" if small else ""), tiles * splits * bm, 2, max(cap, tiles * splits * bm))
+        k.latent_attention_mma(q, out, pool, cu_q, kv_len, table, page_size, tiles, splits, small, heads, width,
+                               rank, scale, part_o, part_ml, err)
+        launches += 1 if splits == 1 else 2
+    return launches
 
 
 _IDENTITY = {}

@@ -33,6 +33,7 @@ def model_folders(tmp_path_factory):
     """Tiny model folders with random weights, made on demand:
     model_folders(name, dtype) -> path."""
     import tiny_configs
+    import tiny_radorax
     from crane_b200.weights.random_init import write_model_folder
     made = {}
 
@@ -40,7 +41,7 @@ def model_folders(tmp_path_factory):
         key = (name, dtype)
         if key not in made:
             d = tmp_path_factory.mktemp(f"{name}_{dtype}")
-            spec = tiny_configs.TINY[name]
+            spec = tiny_configs.TINY[name] if name in tiny_configs.TINY else tiny_radorax.TINY[name]
             write_model_folder(str(d), spec["config"], spec["seed"], dtype, std=spec["std"],
                                norm_std=spec["norm_std"])
             made[key] = str(d)
