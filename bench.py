@@ -426,6 +426,193 @@ def mixed_step_workload(model, cfg, args):
     return res
 
 
+def radorax_config(like, layers):
+    """A Radorax model with the width, head count, layer count and vocabulary of the Hunyuan
+    configuration `like` and about its number of parameters per layer: heads of 128 + 32 (rotated)
+    query/key and 128 value elements, a latent of 192, feed-forward 1.5 x the other's (two matrices
+    instead of three), every layer with a cache of its own."""
+    h, heads = like["hidden_size"], like["num_attention_heads"]
+    mixer = {"heads": heads, "dim": 128, "rot_dim": 32, "vdim": 128, "kv_rank": 192, "scale": 160 ** -0.5,
+             "rot": {"dims": 32, "base": 10000.0,
+                     "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    layer = {"type": "latent_attention", "mixer": mixer,
+             "mlp": {"kind": "dense", "ff": like["intermediate_size"] * 3 // 2}}
+    return {"architecture": "Radorax", "vocab": like["vocab_size"], "width": h, "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 7919}},
+            "layers": [layer] * layers}
+
+
+def _median_ms(fn, reps=9, flush=None):
+    import torch
+    for _ in range(3):
+        fn()
+    out = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.add_(1.0)                      # 512 MB written: L2 holds none of the kernel's inputs
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    out.sort()
+    return out[len(out) // 2]
+
+
+def radorax_kernel_table(rcfg, hcfg, pk, tokens, batch, context):
+    """Every kernel that only Radorax runs beside the kernel of Hunyuan Dense that does the like
+    job, each alone on synthetic operands of the two models' layer sizes (L2 flushed between
+    repetitions), with the fraction of its roofline: algorithmic bytes over the measured copy
+    rate, or FLOPs over the measured bf16 rate, whichever takes longer."""
+    import numpy as np
+    import torch
+    from crane_b200.kernels import get_kernels
+    from crane_b200.parts.latent_attention import latent_attention_kernel
+    K = get_kernels([hcfg["head_dim"]])
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    W, H = rcfg["width"], rcfg["layers"][0]["mixer"]["heads"]
+    m = rcfg["layers"][0]["mixer"]
+    dim, rot, vd, r = m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    ffr, ffh = rcfg["layers"][0]["mlp"]["ff"], hcfg["intermediate_size"]
+    d, nq, nkv = hcfg["head_dim"], hcfg["num_attention_heads"], hcfg["num_key_value_heads"]
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, like, ms, nbytes, flops, like_ms, like_bytes, like_flops):
+        def frac(ms_, b, f):
+            return round(max(b / hbm, f / peak) / (ms_ * 1e-3), 3)
+        rows.append({"kernel": name, "ms": round(ms, 4), "frac": frac(ms, nbytes, flops), "like": like,
+                     "like_ms": round(like_ms, 4) if like_ms else None,
+                     "like_frac": frac(like_ms, like_bytes, like_flops) if like_ms else None})
+
+    T = tokens
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=dev, dtype=torch.float32).to(dt)
+    # the additions and norms between layers, at mid depth (16 earlier results in the average)
+    n_hist = min(17, len(rcfg["layers"]) + 1)
+    x, hist = rnd(T, W, dt=torch.float32), rnd(n_hist, T, W, dt=torch.float32)
+    a, f, o1, o2 = rnd(T, W), rnd(T, W), torch.empty(T, W, device=dev, dtype=bf), torch.empty(T, W, device=dev, dtype=bf)
+    w = [rnd(W, dt=torch.float32) for _ in range(4)]
+    dwa = rnd(n_hist, dt=torch.float32)
+    t_r = _median_ms(lambda: K.combine_layernorm(x, hist, n_hist, a, f, dwa, None, w[0], w[1], o1, w[2], w[3], o2, 1e-5),
+                     flush=flush)
+    t_h = _median_ms(lambda: K.add_rmsnorm(x, a, w[0], 1e-5, o1), flush=flush)
+    add(f"combine_layernorm (average of {n_hist})", "add_rmsnorm", t_r, T * W * (4 * (n_hist + 2) + 2 + 2 + 4), 0,
+        t_h, T * W * (4 + 4 + 2 + 2), 0)
+    del hist
+    # activation
+    up, act = rnd(T, ffr), torch.empty(T, ffr, device=dev, dtype=bf)
+    pq = torch.tensor([0.3, -0.2], device=dev)
+    gu, act_h = rnd(T, 2 * ffh), torch.empty(T, ffh, device=dev, dtype=bf)
+    t_r = _median_ms(lambda: K.xielu(up, act, pq), flush=flush)
+    t_h = _median_ms(lambda: K.silu_mul(gu, act_h, False), flush=flush)
+    add("xielu", "silu_mul", t_r, T * ffr * 4, 0, t_h, T * ffh * 6, 0)
+    del up, act, gu, act_h
+    # attention: one prompt of T tokens, and `batch` decoded tokens at `context`
+    ps = 64
+    for kind, n_req, q_len, kv in (("prefill", 1, T, T), ("decode", batch, 1, context)):
+        blocks = -(-kv // ps)
+        pages = n_req * blocks
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(n_req, blocks)
+        cu = np.arange(n_req + 1, dtype=np.int32) * q_len
+        kvl = np.full(n_req, kv, dtype=np.int32)
+        cu_d, kv_d = torch.from_numpy(cu).to(dev), torch.from_numpy(kvl).to(dev)
+        n = n_req * q_len
+        pos = torch.from_numpy(np.concatenate([np.arange(kv - q_len, kv, dtype=np.int32)] * n_req)).to(dev)
+        ent = torch.from_numpy(np.repeat(np.arange(n_req, dtype=np.int32), q_len)).to(dev)
+        pool = rnd(pages, 1, ps, r + rot)
+        q_abs, o_lat = rnd(n, H * (r + rot)), torch.empty(n, H * r, device=dev, dtype=bf)
+        t_r = _median_ms(lambda: latent_attention_kernel(K, q_abs, o_lat, pool, pos, ent, cu_d, kv_d, cu, kvl, table,
+                                                         ps, H, r, rot, 0.08, err, False), flush=flush)
+        k_pool, v_pool = rnd(pages, nkv, ps, d), rnd(pages, nkv, ps, d)
+        qh, oh = rnd(n, nq * d), torch.empty(n, nq * d, device=dev, dtype=bf)
+        if kind == "prefill":
+            tiles = -(-T // 128)
+            t_h = _median_ms(lambda: K.prefill_attention_tc(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, tiles, nq,
+                                                            nkv, d, 0, d ** -0.5, err), flush=flush)
+            pairs = T * T / 2
+            add("latent_attention_mma (prefill)", "prefill_attn_tc", t_r, 0, pairs * H * 2 * (2 * r + rot),
+                t_h, 0, pairs * nq * 4 * d)
+        else:
+            splits = K.decode_splits(n_req, nkv, 148, 64, max_keys=kv)
+            po = torch.empty(n_req * nq * splits, d, device=dev)
+            pml = torch.empty(n_req * nq * splits, 2, device=dev)
+            t_h = _median_ms(lambda: K.paged_decode_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, nq, nkv,
+                                                              d, 0, d ** -0.5, splits, po, pml, err), flush=flush)
+            add("latent_attention_mma (decode)", "paged_decode_attn", t_r, n_req * kv * (r + rot) * 2, 0,
+                t_h, n_req * kv * nkv * d * 2 * 2, 0)
+        # the two per-head products around the attention (no counterpart: Hunyuan's heads come out of its q/k/v product)
+        if kind == "prefill":
+            cols = H * (dim + rot) + H * vd + r + rot
+            proj = rnd(n, cols)
+            uk, uv_t = rnd(H, dim, r), rnd(H, r, vd)
+            o = torch.empty(n, H * vd, device=dev, dtype=bf)
+            t_q = _median_ms(lambda: K.head_linear(proj, cols, 0, dim + rot, uk, dim, r, q_abs, H * (r + rot), r + rot, H),
+                             flush=flush)
+            t_v = _median_ms(lambda: K.head_linear(o_lat, H * r, 0, r, uv_t, r, vd, o, H * vd, vd, H, gate=proj,
+                                                   g_cols=cols, g_off=H * (dim + rot)), flush=flush)
+            add("head_linear (query into the latent space)", None, t_q, n * H * (dim + r) * 2, 2.0 * n * H * dim * r, 0, 0, 0)
+            add("head_linear (latent output to values, gate)", None, t_v, n * H * (r + 2 * vd) * 2, 2.0 * n * H * r * vd, 0, 0, 0)
+            del proj
+        del pool, k_pool, v_pool
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    return rows
+
+
+def radorax_workload(args, pk):
+    """Prefill and decode throughput of Radorax at the layer sizes of --sizes beside Hunyuan Dense
+    (the engine's closest model) at the same width, heads, layers and vocabulary, random weights,
+    and the kernels of the two side by side."""
+    import gc
+    import torch
+    hcfg = dict(MODEL)
+    hcfg.update(OTHER_SIZES.get(args.sizes, {}))
+    layers = args.layers or hcfg["num_hidden_layers"]
+    hcfg["num_hidden_layers"] = layers
+    hcfg["max_position_embeddings"] = max(hcfg["max_position_embeddings"], args.context + 2048)
+    rcfg = radorax_config(hcfg, layers)
+    page, pt = 64, args.prefill_tokens
+    out = {"workload": "radorax", "sizes": args.sizes, "layers": layers, "batch": args.batch,
+           "context": args.context, "prefill_tokens": pt, "dtype": "bf16", "data": "synthetic", "models": {}}
+    for name, cfg, vocab in (("radorax", rcfg, rcfg["vocab"]), ("hunyuan_dense", hcfg, hcfg["vocab_size"])):
+        opts = dict(page_size=page, num_pages=(args.batch * (args.context + args.steps + args.warmup + 64) + pt) // page + 64,
+                    max_concurrent=max(64, args.batch), max_seq_len=max(args.context, pt) + 1024,
+                    max_batched_tokens=max(2048, pt), chunk_size=max(2048, pt))
+        model = build_model(cfg, opts)
+        pms = time_prefill(model, pt, vocab, reps=3)
+        ids = fill_cache(model, args.batch, args.context)
+        dms, launches = time_decode(model, ids, args.steps, args.warmup, vocab)
+        weights = sum(t.numel() * t.element_size() for t in _model_tensors(model))
+        out["models"][name] = {"prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(pt * 1000.0 / pms, 1),
+                               "decode_ms_per_step": round(dms, 4),
+                               "decode_tokens_per_s": round(args.batch * 1000.0 / dms, 1),
+                               "launches_per_decode_step": launches, "weight_bytes": weights}
+        del model
+        gc.collect()
+        torch.cuda.empty_cache()
+    out["kernels"] = radorax_kernel_table(rcfg, hcfg, pk, pt, args.batch, args.context)
+    out["peaks"] = pk
+    return out
+
+
+def _model_tensors(model):
+    seen, out = set(), []
+    parts = [model.runner.model.embed, model.runner.model.final_norm, model.runner.model.head]
+    for b in model.runner.model.blocks:
+        parts += list(b.parts())
+    import torch
+    for p in parts:
+        for v in vars(p).values():
+            if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                out.append(v)
+    return out
+
+
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "cryptomilk/Crane is a Rust workspace on Candle; there is no cargo or rustc "
@@ -451,9 +638,10 @@ def main():
                     help="layer sizes: Hunyuan 1.8B (the default, the headline configuration), 4B or 7B")
     ap.add_argument("--prefill-chunk", type=int, default=0,
                     help="with --only-prefill: also time the prompt in portions of this many tokens, a step each")
-    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step"],
+    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step", "radorax"],
                     help="serve: a mix of requests through the scheduler; mixed-step: decoded tokens beside "
-                         "one prompt portion in one step; each prints its own record only")
+                         "one prompt portion in one step; radorax: prefill and decode of Radorax beside Hunyuan "
+                         "Dense at equal layer sizes, and their kernels side by side; each prints its own record only")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--prompt-min", type=int, default=128)
     ap.add_argument("--prompt-max", type=int, default=4096)
@@ -472,6 +660,10 @@ def main():
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
     args.warmup = max(args.warmup, 3)
+
+    if args.workload == "radorax":
+        print(json.dumps(radorax_workload(args, peaks())))
+        return 0
 
     import torch
     cfg = dict(MODEL)

@@ -9,7 +9,8 @@
 //               last rot columns go to the token's cache row [rank + rot]; the rotated part of every
 //               query head goes to columns rank.. of the absorbed query [token, head, rank + rot].
 // head_linear   out[t, h, :] = W_h x[t, h, :] for every head (U_h^T on the unrotated query part; V_h on
-//               the attention's latent output, there times sigmoid(gate)), on the FP32 cores.
+//               the attention's latent output, there times sigmoid(gate)): on the FP32 cores in true
+//               32-bit, for partial sums and for a handful of tokens, else on the tensor cores.
 //
 // Rotation: interleaved pairs (2i, 2i + 1) of the leading rot_dims elements of the rotated part,
 // (u, v) -> (u cos - v sin, v cos + u sin); the tables hold cos and sin already scaled.
@@ -132,6 +133,100 @@ head_linear_kernel(GemmOut<T> x, int x_cols, int x_off, int x_head, const T* __r
     }
 }
 
+// ---- the same product on the tensor cores (bf16, warp-level MMA) -------------------------------
+// A CTA takes 64 tokens of one head: the head's matrix [n_in][n_out] and the tokens' inputs come
+// into shared memory by cp.async, each of four warps multiplies 16 tokens by the whole matrix
+// (B fragments by transposed ldmatrix, since the matrix is stored inputs-major), rounds to bf16,
+// applies the gate and writes.  Taken for whole bf16 operands with n_in a multiple of 16 and n_out
+// of 8, both at most 256, and 16-byte aligned rows.
+__device__ __forceinline__ void hl_ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void hl_ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void hl_cp16(void* smem, const void* gmem, bool valid) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a), "l"(gmem), "r"(n));
+}
+
+constexpr int HM_TT = 64;
+template <int MAXK16, int MAXN8>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int x_cols, int x_off, int x_head,
+                       const __nv_bfloat16* __restrict__ w, int n_in, int n_out,
+                       const __nv_bfloat16* __restrict__ gate, int g_cols, int g_off,
+                       const int* __restrict__ tok_entry, __nv_bfloat16* __restrict__ out, int out_pitch,
+                       int out_head, int n_tokens) {
+    extern __shared__ __align__(16) unsigned char hl_smem[];
+    const int lda = n_in + 8, ldw = n_out + 8;
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(hl_smem);      // [64][lda]
+    __nv_bfloat16* w_s = a_s + HM_TT * lda;                               // [n_in][ldw]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int h = blockIdx.y, t0 = blockIdx.x * HM_TT;
+    pdl_launch_dependents();
+    // the head's matrix depends on no earlier kernel
+    const __nv_bfloat16* wh = w + (long long)h * n_in * n_out;
+    for (int r = warp; r < n_in; r += 4)
+        for (int c = lane; c < (n_out >> 3); c += 32) hl_cp16(w_s + r * ldw + c * 8, wh + (long long)r * n_out + c * 8, true);
+    pdl_wait();
+    for (int r = warp; r < HM_TT; r += 4) {
+        const bool ok = t0 + r < n_tokens;
+        const __nv_bfloat16* src = x + (ok ? (long long)(t0 + r) * x_cols + x_off + (long long)h * x_head : 0);
+        for (int c = lane; c < (n_in >> 3); c += 32) hl_cp16(a_s + r * lda + c * 8, src + c * 8, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float acc[MAXN8][4];
+#pragma unroll
+    for (int i = 0; i < MAXN8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const int k16 = n_in >> 4, n8 = n_out >> 3;
+#pragma unroll 1
+    for (int ks = 0; ks < k16; ++ks) {
+        uint32_t a0, a1, a2, a3;
+        hl_ldsm_x4(a0, a1, a2, a3, a_s + (warp * 16 + (lane & 15)) * lda + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int n2 = 0; n2 < MAXN8 / 2; ++n2) {
+            if (2 * n2 < n8) {
+                uint32_t b0, b1, b2, b3;
+                hl_ldsm_x4_t(b0, b1, b2, b3, w_s + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldw + n2 * 16 + (lane >> 4) * 8);
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(acc[2 * n2][0]), "+f"(acc[2 * n2][1]), "+f"(acc[2 * n2][2]), "+f"(acc[2 * n2][3])
+                             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+                if (2 * n2 + 1 < n8)
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[2 * n2 + 1][0]), "+f"(acc[2 * n2 + 1][1]), "+f"(acc[2 * n2 + 1][2]), "+f"(acc[2 * n2 + 1][3])
+                                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b2), "r"(b3));
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int t = t0 + warp * 16 + g + 8 * half;
+        if (t >= n_tokens || (tok_entry != nullptr && tok_entry[t] < 0)) continue;
+        __nv_bfloat16* dst = out + (long long)t * out_pitch + (long long)h * out_head + 2 * t4;
+        const __nv_bfloat16* gp = gate ? gate + (long long)t * g_cols + g_off + (long long)h * n_out + 2 * t4 : nullptr;
+#pragma unroll
+        for (int i = 0; i < MAXN8; ++i) {
+            if (i < n8) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(acc[i][2 * half], acc[i][2 * half + 1]);
+                if (gp != nullptr) {
+                    const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gp + i * 8));
+                    const float2 f = __bfloat1622float2(v);
+                    v = __floats2bfloat162_rn(f.x / (1.f + expf(-gv.x)), f.y / (1.f + expf(-gv.y)));
+                }
+                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = v;
+            }
+        }
+    }
+}
+
 }  // namespace
 
 CRANE_API int crane_latent_prep(int dtype, const void* proj, const float* proj_parts, int n_parts,
@@ -158,6 +253,23 @@ CRANE_API int crane_head_linear(int dtype, const void* x, const float* x_parts, 
                                 int g_cols, int g_off, const int* tok_entry, void* out, int out_pitch,
                                 int out_head, int n_tokens, int heads, cudaStream_t st) {
     if (n_tokens <= 0 || heads <= 0) return 0;
+    const bool aligned = x_cols % 8 == 0 && x_off % 8 == 0 && x_head % 8 == 0 && out_pitch % 2 == 0 &&
+                         out_head % 2 == 0 && g_cols % 2 == 0 && g_off % 2 == 0 &&
+                         ((uintptr_t)x | (uintptr_t)w) % 16 == 0 && ((uintptr_t)out | (uintptr_t)gate) % 4 == 0;
+    if (dtype == 1 && x != nullptr && (gate != nullptr || g_parts == nullptr) && n_tokens > 16 && aligned &&
+        n_in % 16 == 0 && n_out % 8 == 0 && n_in <= 256 && n_out <= 256) {
+        const size_t sm = ((size_t)HM_TT * (n_in + 8) + (size_t)n_in * (n_out + 8)) * sizeof(__nv_bfloat16);
+        auto kern = head_linear_mma_kernel<16, 32>;
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            attr_set = true;
+        }
+        return crane_launch(kern, dim3((n_tokens + HM_TT - 1) / HM_TT, heads), dim3(128), sm, st,
+                            (const __nv_bfloat16*)x, x_cols, x_off, x_head, (const __nv_bfloat16*)w, n_in, n_out,
+                            (const __nv_bfloat16*)gate, g_cols, g_off, tok_entry, (__nv_bfloat16*)out, out_pitch,
+                            out_head, n_tokens);
+    }
     const size_t smem = (size_t)HL_TT * n_in * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     const int has_gate = (gate != nullptr || g_parts != nullptr) ? 1 : 0;

@@ -8,11 +8,14 @@
 // sum, over the leading columns, read transposed).  A decoded token is a tile of H rows; a portion
 // of n tokens has n * H rows in tiles of 64.
 //
-// One kernel, two shapes: 4 warps x 16 rows for entries of more than 16 rows, 1 warp x 16 rows for
-// the others (decoded tokens of up to 16 heads), each launch skipping the other's entries.  The
-// keys of a tile may be cut into `splits` slices (grid.y); every slice leaves (max, sum, weighted
-// sum) in scratch and a second kernel merges them.  Key tiles of 64 rows come in by cp.async
-// through the block table, two buffers.  Scores, softmax statistics and sums are float.
+// One kernel, two shapes, each launch skipping the other's entries.  Entries of more than 16 rows:
+// tiles of 64 rows, 16 per warp, every warp over all keys of a key tile; a request's last tile comes
+// first, since it has the most keys.  Entries of at most 16 rows (decoded tokens of up to 16 heads):
+// one tile of 16 rows that all four warps share, each warp taking 16 of a key tile's 64 keys with
+// running sums of its own, merged through shared memory at the end.  The keys of a tile may be cut
+// into `splits` slices (grid.y); every slice leaves (max, sum, weighted sum) in scratch and a second
+// kernel merges them.  Key tiles of 64 rows come in by cp.async through the block table (a warp per
+// row, one page look-up per row), two buffers.  Scores, softmax statistics and sums are float.
 //
 // Widths are run-time numbers below compile-time bounds (two instantiations: up to 128 + 128 and
 // up to 256 key / 192 value columns); rank + rot a multiple of 16, rank a multiple of 8.
@@ -62,7 +65,7 @@ __device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ cu_q
         const int tiles = (rows + rows_per_tile - 1) / rows_per_tile;
         if (tile < tiles) {
             entry = e;
-            row0 = tile * rows_per_tile;
+            row0 = (small ? tile : tiles - 1 - tile) * rows_per_tile;     // the tile with the most keys first
             return true;
         }
         tile -= tiles;
@@ -70,15 +73,18 @@ __device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ cu_q
     return false;
 }
 
-template <int WARPS, int MAXDK16, int MAXDV8>
-__global__ void __launch_bounds__(WARPS * 32)
+template <bool SMALL, int MAXDK16, int MAXDV8>
+__global__ void __launch_bounds__(128)
 latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        const __nv_bfloat16* __restrict__ pool, const int* __restrict__ cu_q,
                        const int* __restrict__ kv_len, const int* __restrict__ block_table, int max_blocks,
-                       int num_pages, int page_size, int n_entries, int heads, int dk, int dv, float scale,
+                       int num_pages, int page_shift, int n_entries, int heads, int dk, int dv, float scale,
                        int* err) {
-    constexpr int BM = WARPS * 16;
+    constexpr int WARPS = 4;
+    constexpr int BM = SMALL ? 16 : 64;               // query rows of a tile
+    constexpr int NT = SMALL ? 2 : 8;                 // blocks of 8 keys that a warp takes of a key tile
+    const int page_size = 1 << page_shift;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int ld = dk + 8;                            // padded row: ldmatrix without bank conflicts
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [BM][ld]
@@ -88,8 +94,10 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     const int dk16 = dk >> 4, dv8 = dv >> 3;
     pdl_launch_dependents();
     int entry, row0;
-    if (!find_tile(blockIdx.x, cu_q, n_entries, heads, BM, WARPS == 1, entry, row0)) return;
+    if (!find_tile(blockIdx.x, cu_q, n_entries, heads, BM, SMALL, entry, row0)) return;
     const int splits = gridDim.y, split = blockIdx.y;
+    const int wrow = SMALL ? 0 : warp * 16;           // the warp's first row of the tile
+    const int wkey = SMALL ? warp * 16 : 0;           // and its first key of a key tile
     const int q_first = cu_q[entry], q_len = cu_q[entry + 1] - q_first, kv = kv_len[entry];
     const int rows = q_len * heads;
     const int n_rows = min(BM, rows - row0);
@@ -104,31 +112,28 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     pdl_wait();
 
     // the tile's query rows (rows beyond the entry's: zeros)
-    for (int i = threadIdx.x; i < BM * chunks; i += WARPS * 32) {
-        const int r = i / chunks, c = i % chunks;
-        const int row = row0 + r;
+    for (int r = warp; r < BM; r += WARPS) {
         const bool ok = r < n_rows;
-        const long long src = ok ? ((long long)(q_first + row / heads) * heads + row % heads) * dk + c * 8 : 0;
-        cp_async16(q_s + r * ld + c * 8, q + src, ok);
+        const long long src = ok ? ((long long)q_first * heads + row0 + r) * dk : 0;
+        for (int c = lane; c < chunks; c += 32) cp_async16(q_s + r * ld + c * 8, q + src + c * 8, ok);
     }
     bool bad_page = false;
     auto load_keys = [&](int kt, int buf) {
         __nv_bfloat16* dst = k_s + buf * KT * ld;
-        for (int i = threadIdx.x; i < KT * chunks; i += WARPS * 32) {
-            const int r = i / chunks, c = i % chunks;
+        for (int r = warp; r < KT; r += WARPS) {
             const int j = kt * KT + r;
             bool ok = j < n_keys;
             long long src = 0;
             if (ok) {
-                const int page = table[j / page_size];
+                const int page = table[j >> page_shift];
                 if (page < 0 || page >= num_pages) {
                     bad_page = true;
                     ok = false;
                 } else {
-                    src = ((long long)page * page_size + j % page_size) * dk + c * 8;
+                    src = (((long long)page << page_shift) + (j & (page_size - 1))) * dk;
                 }
             }
-            cp_async16(dst + r * ld + c * 8, pool + src, ok);
+            for (int c = lane; c < chunks; c += 32) cp_async16(dst + r * ld + c * 8, pool + src + c * 8, ok);
         }
     };
     if (kt_lo < kt_hi) load_keys(kt_lo, 0);
@@ -139,7 +144,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     for (int i = 0; i < MAXDV8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     // this thread's two rows (g and g + 8 of the warp's 16) and the last key each may see
-    const int r_a = warp * 16 + g, r_b = r_a + 8;
+    const int r_a = wrow + g, r_b = r_a + 8;
     const int see_a = pos0 + (row0 + min(r_a, n_rows - 1)) / heads;
     const int see_b = pos0 + (row0 + min(r_b, n_rows - 1)) / heads;
     const float sl2 = scale * 1.4426950408889634f;   // scores in units of log2 e
@@ -151,29 +156,29 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         cp_async_wait<1>();
         __syncthreads();
         const __nv_bfloat16* kb = k_s + buf * KT * ld;
-        // S = Q K^T for the warp's 16 rows and the tile's 64 keys
-        float s[KT / 8][4];
+        // S = Q K^T for the warp's 16 rows and its keys of the tile
+        float s[NT][4];
 #pragma unroll
-        for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < MAXDK16; ++ks) {
             if (ks < dk16) {
                 uint32_t a0, a1, a2, a3;
-                ldsm_x4(a0, a1, a2, a3, q_s + (warp * 16 + (lane & 15)) * ld + ks * 16 + (lane >> 4) * 8);
+                ldsm_x4(a0, a1, a2, a3, q_s + (wrow + (lane & 15)) * ld + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-                for (int j = 0; j < KT / 16; ++j) {
+                for (int j = 0; j < NT / 2; ++j) {
                     uint32_t b0, b1, b2, b3;
-                    ldsm_x4(b0, b1, b2, b3, kb + (j * 16 + (lane & 7) + (lane >> 4) * 8) * ld + ks * 16 + ((lane >> 3) & 1) * 8);
+                    ldsm_x4(b0, b1, b2, b3, kb + (wkey + j * 16 + (lane & 7) + (lane >> 4) * 8) * ld + ks * 16 + ((lane >> 3) & 1) * 8);
                     mma_bf16(s[2 * j], a0, a1, a2, a3, b0, b1);
                     mma_bf16(s[2 * j + 1], a0, a1, a2, a3, b2, b3);
                 }
             }
         }
         // causal mask, running maximum and sum
-        const int key0 = kt * KT + 2 * t4;
+        const int key0 = kt * KT + wkey + 2 * t4;
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < KT / 8; ++j) {
+        for (int j = 0; j < NT; ++j) {
             const int k0 = key0 + j * 8;
             s[j][0] = k0 <= see_a ? s[j][0] * sl2 : -INFINITY;
             s[j][1] = k0 + 1 <= see_a ? s[j][1] * sl2 : -INFINITY;
@@ -193,7 +198,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         m_run[1] = new_b;
         float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
-        for (int j = 0; j < KT / 8; ++j) {
+        for (int j = 0; j < NT; ++j) {
             s[j][0] = exp2f(s[j][0] - base_a);
             s[j][1] = exp2f(s[j][1] - base_a);
             s[j][2] = exp2f(s[j][2] - base_b);
@@ -212,7 +217,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         }
         // O += P V, V the leading dv columns of the same rows, read transposed
 #pragma unroll
-        for (int kk = 0; kk < KT / 16; ++kk) {
+        for (int kk = 0; kk < NT / 2; ++kk) {
             const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
             const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
@@ -220,7 +225,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
                 if (2 * n2 < dv8) {
                     uint32_t b0, b1, b2, b3;
                     // (a second block of 8 columns beyond dv is still inside the row: dk >= dv + ... or the row's padding)
-                    ldsm_x4_t(b0, b1, b2, b3, kb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + n2 * 16 + (lane >> 4) * 8);
+                    ldsm_x4_t(b0, b1, b2, b3, kb + (wkey + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + n2 * 16 + (lane >> 4) * 8);
                     mma_bf16(o_acc[2 * n2], a0, a1, a2, a3, b0, b1);
                     if (2 * n2 + 1 < MAXDV8 && 2 * n2 + 1 < dv8) mma_bf16(o_acc[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
                 }
@@ -234,6 +239,58 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+
+    if (SMALL) {
+        // the four warps hold sums over different keys of the same 16 rows: warps 1..3 leave theirs in
+        // shared memory (the key buffers are free now), warp 0 adds them to its own in warp order
+        float* xo = reinterpret_cast<float*>(k_s);                  // [3][16][dv]
+        float* xml = xo + 3 * 16 * dv;                              // [3][16][2]
+        if (warp > 0) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = g + 8 * half;
+                float* dst = xo + ((warp - 1) * 16 + r) * dv + 2 * t4;
+#pragma unroll
+                for (int i = 0; i < MAXDV8; ++i)
+                    if (i < dv8) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o_acc[i][2 * half], o_acc[i][2 * half + 1]);
+                if (t4 == 0) {
+                    xml[((warp - 1) * 16 + r) * 2] = m_run[half];
+                    xml[((warp - 1) * 16 + r) * 2 + 1] = l_run[half];
+                }
+            }
+        }
+        __syncthreads();
+        if (warp > 0) return;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = g + 8 * half;
+            float mx = m_run[half];
+            for (int w = 0; w < 3; ++w) mx = fmaxf(mx, xml[(w * 16 + r) * 2]);
+            const float base = mx == -INFINITY ? 0.f : mx;
+            const float mine = exp2f(m_run[half] - base);
+            float wgt[3];
+            float l = l_run[half] * mine;
+            for (int w = 0; w < 3; ++w) {
+                wgt[w] = exp2f(xml[(w * 16 + r) * 2] - base);
+                l = fmaf(wgt[w], xml[(w * 16 + r) * 2 + 1], l);
+            }
+#pragma unroll
+            for (int i = 0; i < MAXDV8; ++i) {
+                if (i < dv8) {
+                    float v0 = o_acc[i][2 * half] * mine, v1 = o_acc[i][2 * half + 1] * mine;
+                    for (int w = 0; w < 3; ++w) {
+                        const float2 o = *reinterpret_cast<const float2*>(xo + (w * 16 + r) * dv + i * 8 + 2 * t4);
+                        v0 = fmaf(wgt[w], o.x, v0);
+                        v1 = fmaf(wgt[w], o.y, v1);
+                    }
+                    o_acc[i][2 * half] = v0;
+                    o_acc[i][2 * half + 1] = v1;
+                }
+            }
+            m_run[half] = mx;
+            l_run[half] = l;
+        }
+    }
 
     if (splits == 1) {
         const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
@@ -270,15 +327,15 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
 }
 
 // out[row] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), over a tile's slices in order.
-template <int WARPS>
+template <bool SMALL>
 __global__ void __launch_bounds__(128)
 latent_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q, int n_entries,
                          int heads, int dv, int splits) {
-    constexpr int BM = WARPS * 16;
+    constexpr int BM = SMALL ? 16 : 64;
     pdl_launch_dependents();
     int entry, row0;
-    if (!find_tile(blockIdx.x, cu_q, n_entries, heads, BM, WARPS == 1, entry, row0)) return;
+    if (!find_tile(blockIdx.x, cu_q, n_entries, heads, BM, SMALL, entry, row0)) return;
     const int q_first = cu_q[entry], rows = (cu_q[entry + 1] - q_first) * heads;
     const int n_rows = min(BM, rows - row0);
     pdl_wait();
@@ -302,18 +359,25 @@ latent_attn_merge_kernel(const float* __restrict__ part_o, const float* __restri
     }
 }
 
-template <int WARPS, int MAXDK16, int MAXDV8>
+template <bool SMALL, int MAXDK16, int MAXDV8>
 int launch(const __nv_bfloat16* q, __nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* pool,
            const int* cu_q, const int* kv_len, const int* block_table, int max_blocks, int num_pages, int page_size,
            int n_entries, int tiles, int splits, int heads, int dk, int dv, float scale, int* err, cudaStream_t st) {
-    constexpr int BM = WARPS * 16;
+    constexpr int BM = SMALL ? 16 : 64;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    if ((1 << page_shift) != page_size) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(BM + 2 * KT) * (dk + 8) * sizeof(__nv_bfloat16);
-    auto kern = latent_attn_mma_kernel<WARPS, MAXDK16, MAXDV8>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    int rc = crane_launch(kern, dim3(tiles, splits), dim3(WARPS * 32), smem, st, q, out, part_o, part_ml, pool, cu_q,
-                          kv_len, block_table, max_blocks, num_pages, page_size, n_entries, heads, dk, dv, scale, err);
+    auto kern = latent_attn_mma_kernel<SMALL, MAXDK16, MAXDV8>;
+    static bool attr_set = false;                    // (one flag per instantiation)
+    if (smem > 48 * 1024 && !attr_set) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_set = true;
+    }
+    int rc = crane_launch(kern, dim3(tiles, splits), dim3(128), smem, st, q, out, part_o, part_ml, pool, cu_q,
+                          kv_len, block_table, max_blocks, num_pages, page_shift, n_entries, heads, dk, dv, scale, err);
     if (rc != 0 || splits == 1) return rc;
-    return crane_launch(latent_attn_merge_kernel<WARPS>, dim3(tiles), dim3(128), 0, st, (const float*)part_o,
+    return crane_launch(latent_attn_merge_kernel<SMALL>, dim3(tiles), dim3(128), 0, st, (const float*)part_o,
                         (const float*)part_ml, out, cu_q, n_entries, heads, dv, splits);
 }
 
@@ -325,7 +389,7 @@ CRANE_API int crane_latent_attention_mma_supports(int dk, int dv) {
 }
 
 // `small` 1: the entries of at most 16 rows (tokens x heads), in tiles of 16 rows; 0: the others, in tiles
-// of 64.  `tiles`: at least the number of such tiles.  splits > 1 needs part_o [tiles * splits * rows per
+// of 64.  Pages of a power of two.  `tiles`: at least the number of such tiles.  splits > 1 needs part_o [tiles * splits * rows per
 // tile * dv] and part_ml [tiles * splits * rows per tile * 2] floats.
 CRANE_API int crane_latent_attention_mma(const void* q, void* out, float* part_o, float* part_ml, const void* pool,
                                          const int* cu_q, const int* kv_len, const int* block_table,
@@ -344,10 +408,10 @@ CRANE_API int crane_latent_attention_mma(const void* q, void* out, float* part_o
                            page_size, n_entries, tiles, splits, heads, dk, dv, scale, err, st)
     const bool narrow = dk <= 128 && dv <= 128;
     if (small) {
-        if (narrow) CRANE_LATENT_LAUNCH(1, 8, 16);
-        CRANE_LATENT_LAUNCH(1, 16, 24);
+        if (narrow) CRANE_LATENT_LAUNCH(true, 8, 16);
+        CRANE_LATENT_LAUNCH(true, 16, 24);
     }
-    if (narrow) CRANE_LATENT_LAUNCH(4, 8, 16);
-    CRANE_LATENT_LAUNCH(4, 16, 24);
+    if (narrow) CRANE_LATENT_LAUNCH(false, 8, 16);
+    CRANE_LATENT_LAUNCH(false, 16, 24);
 #undef CRANE_LATENT_LAUNCH
 }

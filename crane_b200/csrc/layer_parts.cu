@@ -135,6 +135,26 @@ __global__ void xielu_kernel(GemmOut<T> src, T* __restrict__ out, long long n,
     out[i] = from_f32<T>(y);
 }
 
+// the same for a whole bf16 tensor, eight elements (16 bytes) per thread
+__global__ void xielu_bf16x8_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ out,
+                                    long long n8, const float* __restrict__ pq) {
+    pdl_launch_dependents();
+    const float ap = softplus_f(pq[0]), aq = 0.5f + softplus_f(pq[1]);
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+    __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float2 z = __bfloat1622float2(v[k]);
+        z.x = z.x > 0.f ? fmaf(ap * z.x, z.x, 0.5f * z.x) : fmaf(aq, expm1f(z.x) - z.x, 0.5f * z.x);
+        z.y = z.y > 0.f ? fmaf(ap * z.y, z.y, 0.5f * z.y) : fmaf(aq, expm1f(z.y) - z.y, 0.5f * z.y);
+        v[k] = __floats2bfloat162_rn(z.x, z.y);
+    }
+    reinterpret_cast<uint4*>(out)[i] = raw;
+}
+
 CRANE_API int crane_embed_bigram(int dtype, const int* tokens, const void* table, const void* bigram,
                                  float* x, int n_tokens, int hidden, int vocab, int buckets,
                                  long long mul_prev, long long mul_cur, const int* positions,
@@ -176,6 +196,9 @@ CRANE_API int crane_xielu(int dtype, const void* up, const float* up_parts, int 
                           long long part_stride, void* out, long long n, const float* pq,
                           cudaStream_t st) {
     if (n <= 0) return 0;
+    if (dtype == 1 && up != nullptr && n % 8 == 0 && ((uintptr_t)up | (uintptr_t)out) % 16 == 0)
+        return crane_launch(xielu_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st,
+                            (const __nv_bfloat16*)up, (__nv_bfloat16*)out, n / 8, pq);
     DISPATCH_T(dtype, {
         GemmOut<T> src{(const T*)up, up_parts, n_parts, part_stride};
         return crane_launch(xielu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, src,

@@ -14,6 +14,7 @@ runs the model's schedule.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -462,6 +463,11 @@ class ModelRunner:
             before = self.rt.launches
             torch.cuda.synchronize(self.rt.device)
             graph = torch.cuda.CUDAGraph()
+            # Nothing may free device or pinned memory while the stream is capturing (the capture
+            # would be aborted): what the collector could free is freed now, and it rests meanwhile.
+            gc.collect()
+            collecting = gc.isenabled()
+            gc.disable()
             try:
                 with torch.cuda.graph(graph):
                     logits = self.model.forward(ctx, self.pools.layers)
@@ -472,6 +478,9 @@ class ModelRunner:
                     "a step could not be recorded as a CUDA graph; a part that reads results on the "
                     "host in its forward must set `capturable = False` (or run the engine with "
                     "use_cuda_graphs=False)") from exc
+            finally:
+                if collecting:
+                    gc.enable()
             # The step itself has just run, kernel by kernel; the graph serves the later steps of its
             # shape.  (Replaying it now as well would run the step twice, which pages bear, since the
             # same rows get the same values, but a mixer's per-request state does not.)

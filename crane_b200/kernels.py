@@ -107,7 +107,8 @@ class Kernels:
         # kernels of a step overlap their start with the end of the kernel before them
         self.lib.crane_set_pdl.argtypes = [c_int]
         self.lib.crane_set_pdl.restype = None
-        self.lib.crane_set_pdl(0 if os.environ.get("CRANE_PDL", "1") == "0" else 1)
+        self.pdl_default = 0 if os.environ.get("CRANE_PDL", "1") == "0" else 1
+        self.lib.crane_set_pdl(self.pdl_default)
         self.head_sizes = {d for d in build.ATTENTION_HEAD_SIZES
                            if self.lib.crane_paged_decode_attention_supports(d, 1, 1)}
 

@@ -57,6 +57,7 @@ class Runtime:
         # the next one's together are at most this much: they must fit L2 beside each other.
         self.prefetch_cap = int(os.environ.get("CRANE_L2_PREFETCH_MB", "80")) << 20
         self.use_prefetch = os.environ.get("CRANE_L2_PREFETCH", "1") != "0"
+        self._after_product = -1     # the launch count as the last product left it
         self._w_order = []           # (address, bytes) of the step's product weights, in order
         self._w_pos = 0
 
@@ -112,7 +113,22 @@ class Runtime:
             self.kernels.gemm_simt(x, w, bias, out)
             self.launches += 1
             return out
-        return self._linear_bf16(x, w, bias, out, hint_next, name if hold else None)
+        # A many-token product launched straight behind another product (the two branches of a
+        # parallel block: output projection, then the feed-forward's first matrix) does not start
+        # before that one has finished.  With programmatic dependent launch its CTAs could come to
+        # rest on an SM beside a CTA of the running product that has announced its dependents but
+        # not yet taken its tensor memory, take all of it and wait for that product: neither would
+        # end.  (Seen as a prefill of 2,048 tokens that never finished; sequences with a kernel of
+        # another kind between two products, which is all that Hunyuan Dense has, are not affected.)
+        serial = M > self.split_rows and self.launches == self._after_product and self.kernels.pdl_default
+        if serial:
+            self.kernels.lib.crane_set_pdl(0)
+        try:
+            return self._linear_bf16(x, w, bias, out, hint_next, name if hold else None)
+        finally:
+            if serial:
+                self.kernels.lib.crane_set_pdl(1)
+            self._after_product = self.launches
 
     def linear_silu_mul(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
         """out[M, N/2] = silu(gate) * up of x @ w^T in one kernel, for w whose rows

@@ -124,8 +124,11 @@ def test_pools_shape_keys_and_values_independently():
     from crane_b200.cache.pools import bytes_per_page, group_layers
     from crane_b200.parts import CacheNeed
     needs = [CacheNeed("kv", kv_heads=2, head_dim=16), CacheNeed("kv", kv_heads=2, head_dim=16, v_head_dim=40),
-             CacheNeed("none"), CacheNeed("kv", kv_heads=2, head_dim=16), CacheNeed("kv", kv_heads=1, head_dim=24, v_head_dim=8)]
+             CacheNeed("none"), CacheNeed("kv", kv_heads=2, head_dim=16), CacheNeed("kv", kv_heads=1, head_dim=24, v_head_dim=8),
+             # values that are the leading columns of the key rows: no pool of their own
+             CacheNeed("kv", kv_heads=1, head_dim=24, v_head_dim=8, values_in_keys=True)]
     keys, of_layer = group_layers(needs)
-    assert keys == [(2, 16, 0, 16), (2, 16, 0, 40), (1, 24, 0, 8)] and of_layer == [0, 1, -1, 0, 2]
-    assert bytes_per_page(needs, 8, 2) == [2 * (2 * 8 * 32 * 2), 2 * 8 * 56 * 2, 1 * 8 * 32 * 2]
+    assert keys == [(2, 16, 0, 16, False), (2, 16, 0, 40, False), (1, 24, 0, 8, False), (1, 24, 0, 8, True)]
+    assert of_layer == [0, 1, -1, 0, 2, 3]
+    assert bytes_per_page(needs, 8, 2) == [2 * (2 * 8 * 32 * 2), 2 * 8 * 56 * 2, 1 * 8 * 32 * 2, 1 * 8 * 24 * 2]
     assert needs[0].value_dim == 16 and needs[1].value_dim == 40

@@ -191,24 +191,28 @@ def test_embed_bigram_keeps_the_previous_token_per_slot(K):
     assert np.allclose(x.cpu().numpy()[0], table[4] + big[buckets], atol=1e-6) and state.tolist()[2] == 4
 
 
+# (the second and third shapes are ones that the tensor-core kernel takes in bfloat16: aligned rows,
+# 16 | n_in, 8 | n_out, more than 16 tokens; the last fills its bounds)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_head_linear(K, dtype):
+@pytest.mark.parametrize("n, H, n_in, n_out, cols, x_off, x_head, g_off",
+                         [(37, 3, 20, 12, 150, 6, 25, 90), (150, 3, 32, 24, 256, 8, 40, 128),
+                          (70, 2, 256, 256, 1040, 0, 264, 528)])
+def test_head_linear(K, dtype, n, H, n_in, n_out, cols, x_off, x_head, g_off):
     rng = np.random.default_rng(3)
-    n, H, n_in, n_out, cols, x_off, g_off = 37, 3, 20, 12, 150, 6, 90
     src = _dev(rng.standard_normal((n, cols)), dtype)
     w = _dev(rng.standard_normal((H, n_in, n_out)) * 0.3, dtype)
-    out = torch.zeros(n, H * n_out + 5, dtype=dtype, device=DEV)
+    out = torch.zeros(n, H * n_out + 6, dtype=dtype, device=DEV)
     s64, w64 = src.double().cpu().numpy(), w.double().cpu().numpy()
-    xs = np.stack([s64[:, x_off + h * 25: x_off + h * 25 + n_in] for h in range(H)], 1)
+    xs = np.stack([s64[:, x_off + h * x_head: x_off + h * x_head + n_in] for h in range(H)], 1)
     want = np.einsum("thi,hio->tho", xs, w64)
-    K.head_linear(src, cols, x_off, 25, w, n_in, n_out, out, H * n_out + 5, n_out, H)
+    K.head_linear(src, cols, x_off, x_head, w, n_in, n_out, out, H * n_out + 6, n_out, H)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     got = out.double().cpu().numpy()[:, :H * n_out].reshape(n, H, n_out)
     assert np.abs(got - want).max() < tol * np.abs(want).max()
     gate = s64[:, g_off:g_off + H * n_out].reshape(n, H, n_out)
     ent = np.zeros(n, dtype=np.int32)
     ent[5] = -1                                      # a row of no entry is left as it was
-    K.head_linear(src, cols, x_off, 25, w, n_in, n_out, out, H * n_out + 5, n_out, H, tok_entry=_dev(ent, torch.int32),
+    K.head_linear(src, cols, x_off, x_head, w, n_in, n_out, out, H * n_out + 6, n_out, H, tok_entry=_dev(ent, torch.int32),
                   gate=src, g_cols=cols, g_off=g_off)
     got2 = out.double().cpu().numpy()[:, :H * n_out].reshape(n, H, n_out)
     want2 = want / (1 + np.exp(-gate))
