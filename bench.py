@@ -536,6 +536,12 @@ def radorax_kernel_table(rcfg, hcfg, pk, tokens, batch, context):
             pairs = T * T / 2
             add("latent_attention_mma (prefill)", "prefill_attn_tc", t_r, 0, pairs * H * 2 * (2 * r + rot),
                 t_h, 0, pairs * nq * 4 * d)
+            # and beside the engine's own warp-level flash attention (the kernel of the same kind)
+            tiles64 = -(-T // 64)
+            t_w = _median_ms(lambda: K.paged_prefill_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, tiles64,
+                                                               nq, nkv, d, 0, d ** -0.5, err), flush=flush)
+            add("latent_attention_mma (prefill)", "paged_prefill_attn (warp-level MMA)", t_r, 0,
+                pairs * H * 2 * (2 * r + rot), t_w, 0, pairs * nq * 4 * d)
         else:
             splits = K.decode_splits(n_req, nkv, 148, 64, max_keys=kv)
             po = torch.empty(n_req * nq * splits, d, device=dev)

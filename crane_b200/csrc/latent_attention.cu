@@ -9,8 +9,8 @@
 //               last rot columns go to the token's cache row [rank + rot]; the rotated part of every
 //               query head goes to columns rank.. of the absorbed query [token, head, rank + rot].
 // head_linear   out[t, h, :] = W_h x[t, h, :] for every head (U_h^T on the unrotated query part; V_h on
-//               the attention's latent output, there times sigmoid(gate)): on the FP32 cores in true
-//               32-bit, for partial sums and for a handful of tokens, else on the tensor cores.
+//               the attention's latent output, there times sigmoid(gate)): on the tensor cores in
+//               bfloat16 (widths that the MMA tiles take), else on the FP32 cores.
 //
 // Rotation: interleaved pairs (2i, 2i + 1) of the leading rot_dims elements of the rotated part,
 // (u, v) -> (u cos - v sin, v cos + u sin); the tables hold cos and sin already scaled.
@@ -137,8 +137,8 @@ head_linear_kernel(GemmOut<T> x, int x_cols, int x_off, int x_head, const T* __r
 // A CTA takes 64 tokens of one head: the head's matrix [n_in][n_out] and the tokens' inputs come
 // into shared memory by cp.async, each of four warps multiplies 16 tokens by the whole matrix
 // (B fragments by transposed ldmatrix, since the matrix is stored inputs-major), rounds to bf16,
-// applies the gate and writes.  Taken for whole bf16 operands with n_in a multiple of 16 and n_out
-// of 8, both at most 256, and 16-byte aligned rows.
+// applies the gate and writes.  Taken for bf16 with n_in a multiple of 16 and n_out of 8, both at
+// most 256, and 16-byte aligned rows; operands left as partial sums are added up on the way in.
 __device__ __forceinline__ void hl_ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -158,9 +158,9 @@ __device__ __forceinline__ void hl_cp16(void* smem, const void* gmem, bool valid
 constexpr int HM_TT = 64;
 template <int MAXK16, int MAXN8>
 __global__ void __launch_bounds__(128)
-head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int x_cols, int x_off, int x_head,
+head_linear_mma_kernel(GemmOut<__nv_bfloat16> x, int x_cols, int x_off, int x_head,
                        const __nv_bfloat16* __restrict__ w, int n_in, int n_out,
-                       const __nv_bfloat16* __restrict__ gate, int g_cols, int g_off,
+                       GemmOut<__nv_bfloat16> gate, int has_gate, int g_cols, int g_off,
                        const int* __restrict__ tok_entry, __nv_bfloat16* __restrict__ out, int out_pitch,
                        int out_head, int n_tokens) {
     extern __shared__ __align__(16) unsigned char hl_smem[];
@@ -177,8 +177,15 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int x_cols, int x_of
     pdl_wait();
     for (int r = warp; r < HM_TT; r += 4) {
         const bool ok = t0 + r < n_tokens;
-        const __nv_bfloat16* src = x + (ok ? (long long)(t0 + r) * x_cols + x_off + (long long)h * x_head : 0);
-        for (int c = lane; c < (n_in >> 3); c += 32) hl_cp16(a_s + r * lda + c * 8, src + c * 8, ok);
+        const long long at = ok ? (long long)(t0 + r) * x_cols + x_off + (long long)h * x_head : 0;
+        if (x.parts == nullptr) {
+            for (int c = lane; c < (n_in >> 3); c += 32) hl_cp16(a_s + r * lda + c * 8, x.whole + at + c * 8, ok);
+        } else {                                        // partial sums: added up and rounded here
+            for (int c = lane; c < (n_in >> 1); c += 32) {
+                const float2 v = ok ? x.load2(at + 2 * c) : make_float2(0.f, 0.f);
+                *reinterpret_cast<__nv_bfloat162*>(a_s + r * lda + 2 * c) = __floats2bfloat162_rn(v.x, v.y);
+            }
+        }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -211,13 +218,13 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int x_cols, int x_of
         const int t = t0 + warp * 16 + g + 8 * half;
         if (t >= n_tokens || (tok_entry != nullptr && tok_entry[t] < 0)) continue;
         __nv_bfloat16* dst = out + (long long)t * out_pitch + (long long)h * out_head + 2 * t4;
-        const __nv_bfloat16* gp = gate ? gate + (long long)t * g_cols + g_off + (long long)h * n_out + 2 * t4 : nullptr;
+        const long long gp = (long long)t * g_cols + g_off + (long long)h * n_out + 2 * t4;
 #pragma unroll
         for (int i = 0; i < MAXN8; ++i) {
             if (i < n8) {
                 __nv_bfloat162 v = __floats2bfloat162_rn(acc[i][2 * half], acc[i][2 * half + 1]);
-                if (gp != nullptr) {
-                    const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gp + i * 8));
+                if (has_gate) {
+                    const float2 gv = gate.load2(gp + i * 8);
                     const float2 f = __bfloat1622float2(v);
                     v = __floats2bfloat162_rn(f.x / (1.f + expf(-gv.x)), f.y / (1.f + expf(-gv.y)));
                 }
@@ -256,8 +263,7 @@ CRANE_API int crane_head_linear(int dtype, const void* x, const float* x_parts, 
     const bool aligned = x_cols % 8 == 0 && x_off % 8 == 0 && x_head % 8 == 0 && out_pitch % 2 == 0 &&
                          out_head % 2 == 0 && g_cols % 2 == 0 && g_off % 2 == 0 &&
                          ((uintptr_t)x | (uintptr_t)w) % 16 == 0 && ((uintptr_t)out | (uintptr_t)gate) % 4 == 0;
-    if (dtype == 1 && x != nullptr && (gate != nullptr || g_parts == nullptr) && n_tokens > 16 && aligned &&
-        n_in % 16 == 0 && n_out % 8 == 0 && n_in <= 256 && n_out <= 256) {
+    if (dtype == 1 && aligned && n_in % 16 == 0 && n_out % 8 == 0 && n_in <= 256 && n_out <= 256) {
         const size_t sm = ((size_t)HM_TT * (n_in + 8) + (size_t)n_in * (n_out + 8)) * sizeof(__nv_bfloat16);
         auto kern = head_linear_mma_kernel<16, 32>;
         static bool attr_set = false;
@@ -265,10 +271,12 @@ CRANE_API int crane_head_linear(int dtype, const void* x, const float* x_parts, 
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             attr_set = true;
         }
-        return crane_launch(kern, dim3((n_tokens + HM_TT - 1) / HM_TT, heads), dim3(128), sm, st,
-                            (const __nv_bfloat16*)x, x_cols, x_off, x_head, (const __nv_bfloat16*)w, n_in, n_out,
-                            (const __nv_bfloat16*)gate, g_cols, g_off, tok_entry, (__nv_bfloat16*)out, out_pitch,
-                            out_head, n_tokens);
+        GemmOut<__nv_bfloat16> gx{(const __nv_bfloat16*)x, x_parts, x_n, x_stride};
+        GemmOut<__nv_bfloat16> gg{(const __nv_bfloat16*)gate, g_parts, g_n, g_stride};
+        return crane_launch(kern, dim3((n_tokens + HM_TT - 1) / HM_TT, heads), dim3(128), sm, st, gx, x_cols, x_off,
+                            x_head, (const __nv_bfloat16*)w, n_in, n_out, gg,
+                            (gate != nullptr || g_parts != nullptr) ? 1 : 0, g_cols, g_off, tok_entry,
+                            (__nv_bfloat16*)out, out_pitch, out_head, n_tokens);
     }
     const size_t smem = (size_t)HL_TT * n_in * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;

@@ -327,35 +327,49 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
 }
 
 // out[row] = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m), over a tile's slices in order.
+// A CTA per (tile, row): the slices' weights once, in shared memory, then a thread per column.
+constexpr int MAX_SPLITS = 64;
 template <bool SMALL>
 __global__ void __launch_bounds__(128)
 latent_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q, int n_entries,
                          int heads, int dv, int splits) {
     constexpr int BM = SMALL ? 16 : 64;
+    __shared__ float wgt[MAX_SPLITS];
+    __shared__ float inv_den;
     pdl_launch_dependents();
     int entry, row0;
     if (!find_tile(blockIdx.x, cu_q, n_entries, heads, BM, SMALL, entry, row0)) return;
     const int q_first = cu_q[entry], rows = (cu_q[entry + 1] - q_first) * heads;
-    const int n_rows = min(BM, rows - row0);
+    const int r = blockIdx.y;
+    if (row0 + r >= rows) return;
     pdl_wait();
-    for (int i = threadIdx.x; i < n_rows * dv; i += blockDim.x) {
-        const int r = i / dv, c = i % dv;
+    const long long first = ((long long)blockIdx.x * splits) * BM + r;       // slice s: first + s * BM
+    if (threadIdx.x < 32) {
         float mx = -INFINITY;
-        for (int s = 0; s < splits; ++s)
-            mx = fmaxf(mx, part_ml[(((long long)blockIdx.x * splits + s) * BM + r) * 2]);
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const long long at = ((long long)blockIdx.x * splits + s) * BM + r;
-            const float m = part_ml[at * 2];
-            if (m == -INFINITY) continue;
-            const float w = exp2f(m - mx);
-            num = fmaf(w, part_o[at * dv + c], num);
-            den = fmaf(w, part_ml[at * 2 + 1], den);
+        for (int s = threadIdx.x; s < splits; s += 32) mx = fmaxf(mx, part_ml[(first + (long long)s * BM) * 2]);
+        mx = warp_max(mx);
+        float den = 0.f;
+        for (int s = threadIdx.x; s < splits; s += 32) {
+            const float m = part_ml[(first + (long long)s * BM) * 2];
+            const float w = m == -INFINITY ? 0.f : exp2f(m - mx);
+            wgt[s] = w;
+            den = fmaf(w, part_ml[(first + (long long)s * BM) * 2 + 1], den);
         }
-        const int row = row0 + r;
-        out[((long long)(q_first + row / heads) * heads + row % heads) * dv + c] =
-            __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        den = warp_sum(den);
+        if (threadIdx.x == 0) inv_den = den > 0.f ? 1.f / den : 0.f;
+    }
+    __syncthreads();
+    const int row = row0 + r;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float num = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) {
+            const float w = wgt[s];
+            const float v = part_o[(first + (long long)s * BM) * dv + c];     // (an empty slice left nothing here)
+            num += w != 0.f ? w * v : 0.f;
+        }
+        out[((long long)q_first * heads + row) * dv + c] = __float2bfloat16_rn(num * inv_den);
     }
 }
 
@@ -377,7 +391,7 @@ int launch(const __nv_bfloat16* q, __nv_bfloat16* out, float* part_o, float* par
     int rc = crane_launch(kern, dim3(tiles, splits), dim3(128), smem, st, q, out, part_o, part_ml, pool, cu_q,
                           kv_len, block_table, max_blocks, num_pages, page_shift, n_entries, heads, dk, dv, scale, err);
     if (rc != 0 || splits == 1) return rc;
-    return crane_launch(latent_attn_merge_kernel<SMALL>, dim3(tiles), dim3(128), 0, st, (const float*)part_o,
+    return crane_launch(latent_attn_merge_kernel<SMALL>, dim3(tiles, BM), dim3(128), 0, st, (const float*)part_o,
                         (const float*)part_ml, out, cu_q, n_entries, heads, dv, splits);
 }
 
@@ -397,7 +411,7 @@ CRANE_API int crane_latent_attention_mma(const void* q, void* out, float* part_o
                                          int splits, int small, int heads, int dk, int dv, float scale, int* err,
                                          cudaStream_t st) {
     if (tiles <= 0 || n_entries <= 0) return 0;
-    if (!crane_latent_attention_mma_supports(dk, dv) || splits < 1 || splits > 65535 ||
+    if (!crane_latent_attention_mma_supports(dk, dv) || splits < 1 || splits > MAX_SPLITS ||
         (splits > 1 && (part_o == nullptr || part_ml == nullptr)))
         return (int)cudaErrorInvalidValue;
     const auto* qb = (const __nv_bfloat16*)q;

@@ -83,25 +83,45 @@ combine_layernorm_kernel(float* __restrict__ x, float* __restrict__ hist, long l
     const int row = rows ? rows[r] : r;
     const long long base = (long long)row * hidden;
     float sum = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float xn = x[base + c];
-        if (has_a || has_f) {
-            float branches = has_a ? a.load(base + c) : 0.f;
-            if (has_f) branches = has_a ? branches + f.load(base + c) : f.load(base + c);
-            xn += branches;
+    // four columns per thread and pass, so that the loads of the earlier results (one per history
+    // entry and column, independent of one another) are in flight together
+    for (int c0 = threadIdx.x * 4; c0 < hidden; c0 += blockDim.x * 4) {
+        const int nc = min(4, hidden - c0);
+        float xn[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            xn[k] = 0.f;
+            if (k < nc) {
+                xn[k] = x[base + c0 + k];
+                if (has_a || has_f) {
+                    float branches = has_a ? a.load(base + c0 + k) : 0.f;
+                    if (has_f) branches = has_a ? branches + f.load(base + c0 + k) : f.load(base + c0 + k);
+                    xn[k] += branches;
+                }
+            }
         }
-        float val = xn;
         if (dwa != nullptr) {
-            float acc = 0.f;
-            for (int j = 0; j + 1 < n_hist; ++j) acc = fmaf(dwa[j], hist[j * hist_stride + base + c], acc);
-            val = fmaf(dwa[n_hist - 1], xn, acc);
+#pragma unroll 4
+            for (int j = 0; j + 1 < n_hist; ++j) {
+                const float wj = dwa[j];
+                const float* hp = hist + j * hist_stride + base + c0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (k < nc) acc[k] = fmaf(wj, hp[k], acc[k]);
+            }
         }
-        if (rows == nullptr) {
-            if (hist != nullptr) hist[(long long)(n_hist - 1) * hist_stride + base + c] = xn;
-            x[base + c] = val;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (k >= nc) break;
+            const int c = c0 + k;
+            const float val = dwa != nullptr ? fmaf(dwa[n_hist - 1], xn[k], acc[k]) : xn[k];
+            if (rows == nullptr) {
+                if (hist != nullptr) hist[(long long)(n_hist - 1) * hist_stride + base + c] = xn[k];
+                x[base + c] = val;
+            }
+            vals[c] = val;
+            sum += val;
         }
-        vals[c] = val;
-        sum += val;
     }
     const float mean = block_sum(sum, scratch) / (float)hidden;
     float sq = 0.f;

@@ -209,6 +209,17 @@ def test_head_linear(K, dtype, n, H, n_in, n_out, cols, x_off, x_head, g_off):
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     got = out.double().cpu().numpy()[:, :H * n_out].reshape(n, H, n_out)
     assert np.abs(got - want).max() < tol * np.abs(want).max()
+    if cols % 8 == 0:
+        # the operand left as two partial sums (a product cut along its inner dimension)
+        from crane_b200.kernels import Partials
+        half = _dev(rng.standard_normal((n, cols)))
+        parts = torch.stack([half, src.float() - half]).contiguous()
+        x2 = parts.sum(0).to(dtype).double().cpu().numpy()
+        xs2 = np.stack([x2[:, x_off + h * x_head: x_off + h * x_head + n_in] for h in range(H)], 1)
+        out2 = torch.zeros_like(out)
+        K.head_linear(Partials(parts), cols, x_off, x_head, w, n_in, n_out, out2, H * n_out + 6, n_out, H)
+        got_p = out2.double().cpu().numpy()[:, :H * n_out].reshape(n, H, n_out)
+        assert np.abs(got_p - np.einsum("thi,hio->tho", xs2, w64)).max() < tol * np.abs(want).max()
     gate = s64[:, g_off:g_off + H * n_out].reshape(n, H, n_out)
     ent = np.zeros(n, dtype=np.int32)
     ent[5] = -1                                      # a row of no entry is left as it was
