@@ -18,7 +18,7 @@ from typing import List, Optional
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="crane", description="Hunyuan Dense generation on one B200")
+    ap = argparse.ArgumentParser(prog="crane", description="generation from a model folder on one B200 (the architecture is chosen by config.json)")
     ap.add_argument("-m", "--model-path", required=True,
                     help="folder with config.json (and safetensors unless --random-weights)")
     ap.add_argument("--model-type", default="auto", help="auto, or a registered architecture/alias")

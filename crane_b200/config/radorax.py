@@ -195,6 +195,12 @@ def build_spec(cfg: RadoraxConfig):
                  "combine": PartSpec("combine", "depth_average",
                                      {"index": i, "slots": n_layers + 1, "size": cfg.width, "weight": "dwa"},
                                      prefix=p)}
+        if layer.mixer.kv_from is not None:
+            for name in ("mix.dkv", "mix.dkv.norm"):
+                ignored[p + name] = "layer reads another layer's cache"
+        if layer.mlp is None:
+            for name in ("norm2", "norm2.b"):
+                ignored[p + name] = "layer has no feed-forward"
         if layer.mlp is not None:
             parts["norm2"] = norm("norm2")
             parts["ffn"] = PartSpec("ffn", "xielu_mlp", {"hidden_size": cfg.width,

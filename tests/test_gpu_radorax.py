@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 LENGTHS = {"RA": [1, 2, 19, 100, 65, 48, 33], "RB": [5, 41, 97, 230, 129, 64], "RC": [3, 70, 130],
-           "RL": [7, 150, 300, 64]}
+           "RL": [7, 150, 300, 64], "RH": [2, 90, 200, 33]}
 
 
 @pytest.fixture(scope="module")
@@ -34,7 +34,7 @@ def cases(model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["RA", "RB", "RC"])
+@pytest.mark.parametrize("name", ["RA", "RB", "RC", "RH"])
 def test_alone_whole_tail_portions(name, dtype, cases, tmp_path):
     folder, reqs, plain = cases(name, dtype)
     ps = tr.TINY[name]["page_size"]
@@ -48,7 +48,7 @@ def test_alone_whole_tail_portions(name, dtype, cases, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["RA", "RB"])
+@pytest.mark.parametrize("name", ["RA", "RB", "RH"])
 def test_mixed_with_page_and_slot_reuse(name, dtype, cases, tmp_path):
     folder, reqs, plain = cases(name, dtype)
     ps = tr.TINY[name]["page_size"]

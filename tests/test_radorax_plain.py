@@ -39,6 +39,9 @@ def test_layout_and_manifest():
     ma = model_manifest(_spec(tr.RA))
     assert "l2.norm2" not in ma and "l2.mlp.up" not in ma and "l2.norm1.b" in ma
     assert "bigram" not in model_manifest(_spec(tr.RC))
+    # tensors that a folder may hold for parts that a layer does not have are passed over
+    ignored = _spec(tr.RA).ignored_tensors
+    assert "l2.norm2" in ignored and "l1.mix.dkv" in ignored and "l0.norm2" not in ignored
 
 
 @pytest.mark.parametrize("change, word", [

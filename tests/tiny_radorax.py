@@ -65,9 +65,22 @@ RL = {
     ],
 }
 
+# more heads than a 16-row tile holds: decoded tokens take the 64-row tiles; the second layer without
+# feed-forward reads the first one's cache
+RH = {
+    "architecture": "Radorax", "vocab": 150, "width": 96, "norm": {"eps": 1e-5},
+    "embedding": {"bigram": {"buckets": 53, "mul_prev": 17, "mul_cur": 3}},
+    "layers": [
+        {"type": "latent_attention", "mixer": _mixer(20, 16, 16, 8, 32, 16, 5000.0, _YA, 0.18),
+         "mlp": {"kind": "dense", "ff": 64}},
+        {"type": "latent_attention", "mixer": _mixer(18, 8, 16, 16, 32, 16, 5000.0, _YA, 0.2, kv_from=0), "mlp": None},
+    ],
+}
+
 TINY = {
     "RA": {"config": RA, "seed": 11, "std": 0.08, "norm_std": 0.05, "page_size": 16},
     "RB": {"config": RB, "seed": 12, "std": 0.06, "norm_std": 0.05, "page_size": 8},
     "RC": {"config": RC, "seed": 13, "std": 0.1, "norm_std": 0.05, "page_size": 64},
     "RL": {"config": RL, "seed": 14, "std": 0.03, "norm_std": 0.05, "page_size": 64},
+    "RH": {"config": RH, "seed": 15, "std": 0.08, "norm_std": 0.05, "page_size": 32},
 }
