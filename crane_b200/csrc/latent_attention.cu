@@ -175,7 +175,14 @@ head_linear_mma_kernel(GemmOut<__nv_bfloat16> x, int x_cols, int x_off, int x_he
     for (int r = warp; r < n_in; r += 4)
         for (int c = lane; c < (n_out >> 3); c += 32) hl_cp16(w_s + r * ldw + c * 8, wh + (long long)r * n_out + c * 8, true);
     pdl_wait();
-    for (int r = warp; r < HM_TT; r += 4) {
+    // At most 16 tokens in the tile (a decode step): the four warps share the one block of 16 rows and
+    // take a quarter of the output columns each, instead of a block of rows each.
+    const bool few = n_tokens - t0 <= 16;
+    const int wrow = few ? 0 : warp * 16;
+    const int n16 = (n_out + 15) >> 4;                              // pairs of 8 output columns
+    const int per = few ? (n16 + 3) >> 2 : n16;
+    const int n2_lo = few ? warp * per : 0, n2_hi = min(n16, n2_lo + per);
+    for (int r = warp; r < (few ? 16 : HM_TT); r += 4) {
         const bool ok = t0 + r < n_tokens;
         const long long at = ok ? (long long)(t0 + r) * x_cols + x_off + (long long)h * x_head : 0;
         if (x.parts == nullptr) {
@@ -197,10 +204,10 @@ head_linear_mma_kernel(GemmOut<__nv_bfloat16> x, int x_cols, int x_off, int x_he
 #pragma unroll 1
     for (int ks = 0; ks < k16; ++ks) {
         uint32_t a0, a1, a2, a3;
-        hl_ldsm_x4(a0, a1, a2, a3, a_s + (warp * 16 + (lane & 15)) * lda + ks * 16 + (lane >> 4) * 8);
+        hl_ldsm_x4(a0, a1, a2, a3, a_s + (wrow + (lane & 15)) * lda + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int n2 = 0; n2 < MAXN8 / 2; ++n2) {
-            if (2 * n2 < n8) {
+            if (n2 >= n2_lo && n2 < n2_hi) {
                 uint32_t b0, b1, b2, b3;
                 hl_ldsm_x4_t(b0, b1, b2, b3, w_s + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldw + n2 * 16 + (lane >> 4) * 8);
                 asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -215,13 +222,13 @@ head_linear_mma_kernel(GemmOut<__nv_bfloat16> x, int x_cols, int x_off, int x_he
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-        const int t = t0 + warp * 16 + g + 8 * half;
+        const int t = t0 + wrow + g + 8 * half;
         if (t >= n_tokens || (tok_entry != nullptr && tok_entry[t] < 0)) continue;
         __nv_bfloat16* dst = out + (long long)t * out_pitch + (long long)h * out_head + 2 * t4;
         const long long gp = (long long)t * g_cols + g_off + (long long)h * n_out + 2 * t4;
 #pragma unroll
         for (int i = 0; i < MAXN8; ++i) {
-            if (i < n8) {
+            if (i < n8 && (i >> 1) >= n2_lo && (i >> 1) < n2_hi) {
                 __nv_bfloat162 v = __floats2bfloat162_rn(acc[i][2 * half], acc[i][2 * half + 1]);
                 if (has_gate) {
                     const float2 gv = gate.load2(gp + i * 8);

@@ -68,7 +68,7 @@ embed_bigram_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
 // rows == nullptr: row r = blockIdx.x, x and hist are updated.  rows != nullptr: row = rows[r] is
 // read, nothing but out1 / out2 [r] is written (the final norm over the wanted rows).
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 combine_layernorm_kernel(float* __restrict__ x, float* __restrict__ hist, long long hist_stride,
                          int n_hist, GemmOut<T> a, int has_a, GemmOut<T> f, int has_f,
                          const float* __restrict__ dwa, const int* __restrict__ rows,
@@ -206,7 +206,12 @@ CRANE_API int crane_combine_layernorm(int dtype, float* x, float* hist, long lon
                                  (int)smem);
         GemmOut<T> ga{(const T*)a, a_parts, a_n, a_stride};
         GemmOut<T> gf{(const T*)f, f_parts, f_n, f_stride};
-        return crane_launch(combine_layernorm_kernel<T>, dim3(n_rows), dim3(256), smem, st, x, hist,
+        // four columns per thread in one pass where the row allows it (few rows: a step of decoded
+        // tokens, where a row's chain of loads is all there is to wait for)
+        int threads = (hidden / 4 + 31) / 32 * 32;
+        threads = threads < 128 ? 128 : threads > 1024 ? 1024 : threads;
+        if (n_rows > 512 && threads > 256) threads = 256;
+        return crane_launch(combine_layernorm_kernel<T>, dim3(n_rows), dim3(threads), smem, st, x, hist,
                             hist_stride, n_hist, ga, has_a, gf, has_f, dwa, rows, w1, b1, (T*)out1, w2, b2,
                             (T*)out2, hidden, eps);
     });

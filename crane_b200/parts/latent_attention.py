@@ -164,11 +164,12 @@ def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len,
         if tiles == 0:
             continue
         bm = 16 if small else 64
-        # slices: enough CTAs to fill the device (twice over for the one-warp tiles), none of fewer than 128 keys
-        splits = max(1, min(32 if small else 8, ((2 if small else 1) * num_sms) // tiles, -(-most_keys // 128)))
+        # slices: enough CTAs to fill the device (four times over for the 16-row tiles, whose CTAs are
+        # short chains of dependent steps), none of fewer than 128 keys
+        splits = max(1, min(64 if small else 8, ((4 if small else 1) * num_sms) // tiles, -(-most_keys // 128)))
         part_o = part_ml = None
         if splits > 1:
-            cap = (max_small * 16 * 32) if small else (num_sms + 1) * 64
+            cap = (max_small * 16 * 64) if small else (num_sms + 1) * 64
             part_o = scratch("latent_part_o" + ("_s" if small else ""), tiles * splits * bm, rank, max(cap, tiles * splits * bm))
             part_ml = scratch("latent_part_ml" + ("_s" if small else ""), tiles * splits * bm, 2, max(cap, tiles * splits * bm))
         k.latent_attention_mma(q, out, pool, cu_q, kv_len, table, page_size, tiles, splits, small, heads, width,
