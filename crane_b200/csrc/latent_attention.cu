@@ -156,7 +156,7 @@ __device__ __forceinline__ void hl_cp16(void* smem, const void* gmem, bool valid
 }
 
 constexpr int HM_TT = 64;
-template <int MAXK16, int MAXN8>
+template <int MAXK16, int MAXN8, bool FEW>
 __global__ void __launch_bounds__(128)
 head_linear_mma_kernel(GemmOut<__nv_bfloat16> x, int x_cols, int x_off, int x_head,
                        const __nv_bfloat16* __restrict__ w, int n_in, int n_out,
@@ -177,7 +177,7 @@ head_linear_mma_kernel(GemmOut<__nv_bfloat16> x, int x_cols, int x_off, int x_he
     pdl_wait();
     // At most 16 tokens in the tile (a decode step): the four warps share the one block of 16 rows and
     // take a quarter of the output columns each, instead of a block of rows each.
-    const bool few = n_tokens - t0 <= 16;
+    constexpr bool few = FEW;                                       // (the launch has 16 tokens at most)
     const int wrow = few ? 0 : warp * 16;
     const int n16 = (n_out + 15) >> 4;                              // pairs of 8 output columns
     const int per = few ? (n16 + 3) >> 2 : n16;
@@ -272,10 +272,11 @@ CRANE_API int crane_head_linear(int dtype, const void* x, const float* x_parts, 
                          ((uintptr_t)x | (uintptr_t)w) % 16 == 0 && ((uintptr_t)out | (uintptr_t)gate) % 4 == 0;
     if (dtype == 1 && aligned && n_in % 16 == 0 && n_out % 8 == 0 && n_in <= 256 && n_out <= 256) {
         const size_t sm = ((size_t)HM_TT * (n_in + 8) + (size_t)n_in * (n_out + 8)) * sizeof(__nv_bfloat16);
-        auto kern = head_linear_mma_kernel<16, 32>;
+        auto kern = n_tokens <= 16 ? head_linear_mma_kernel<16, 32, true> : head_linear_mma_kernel<16, 32, false>;
         static bool attr_set = false;
         if (!attr_set) {
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             attr_set = true;
         }
         GemmOut<__nv_bfloat16> gx{(const __nv_bfloat16*)x, x_parts, x_n, x_stride};

@@ -10,9 +10,9 @@
 //
 // One kernel, two shapes, each launch skipping the other's entries.  Entries of more than 16 rows:
 // tiles of 64 rows, 16 per warp, every warp over all keys of a key tile; a request's last tile comes
-// first, since it has the most keys.  Entries of at most 16 rows (decoded tokens of up to 16 heads):
-// one tile of 16 rows that all four warps share, each warp taking 16 of a key tile's 64 keys with
-// running sums of its own, merged through shared memory at the end.  The keys of a tile may be cut
+// first, since it has the most keys.  Entries of one token (a decoded token: its heads in tiles of 16)
+// or of at most 16 rows: tiles of 16 rows that all four warps share, each warp taking 16 of a key
+// tile's 64 keys with running sums of its own, merged through shared memory at the end.  The keys of a tile may be cut
 // into `splits` slices (grid.y); every slice leaves (max, sum, weighted sum) in scratch and a second
 // kernel merges them.  Key tiles of 64 rows come in by cp.async through the block table (a warp per
 // row, one page look-up per row), two buffers.  Scores, softmax statistics and sums are float.
@@ -55,13 +55,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// The tile'th query tile among the entries that this launch takes (small: entries of at most 16
-// rows; else the others): its entry and first row.  False beyond the last one.
+// The tile'th query tile among the entries that this launch takes (small: entries of one token or
+// of at most 16 rows; else the others): its entry and first row.  False beyond the last one.
 __device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ cu_q, int n_entries, int heads,
                                           int rows_per_tile, bool small, int& entry, int& row0) {
     for (int e = 0; e < n_entries; ++e) {
-        const int rows = (cu_q[e + 1] - cu_q[e]) * heads;
-        if (rows <= 0 || (rows <= 16) != small) continue;
+        const int q_len = cu_q[e + 1] - cu_q[e], rows = q_len * heads;
+        if (rows <= 0 || (q_len == 1 || rows <= 16) != small) continue;
         const int tiles = (rows + rows_per_tile - 1) / rows_per_tile;
         if (tile < tiles) {
             entry = e;
@@ -402,8 +402,8 @@ CRANE_API int crane_latent_attention_mma_supports(int dk, int dv) {
     return dk > 0 && dv > 0 && dk % 16 == 0 && dv % 8 == 0 && dv <= dk && dk <= 256 && dv <= 192 ? 1 : 0;
 }
 
-// `small` 1: the entries of at most 16 rows (tokens x heads), in tiles of 16 rows; 0: the others, in tiles
-// of 64.  Pages of a power of two.  `tiles`: at least the number of such tiles.  splits > 1 needs part_o [tiles * splits * rows per
+// `small` 1: the entries of one token or of at most 16 rows (tokens x heads), in tiles of 16 rows; 0: the
+// others, in tiles of 64.  Pages of a power of two.  `tiles`: at least the number of such tiles.  splits > 1 needs part_o [tiles * splits * rows per
 // tile * dv] and part_ml [tiles * splits * rows per tile * 2] floats.
 CRANE_API int crane_latent_attention_mma(const void* q, void* out, float* part_o, float* part_ml, const void* pool,
                                          const int* cu_q, const int* kv_len, const int* block_table,

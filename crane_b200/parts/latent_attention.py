@@ -138,8 +138,8 @@ def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len,
     """out [N, heads * rank] = attention of q [N, heads * (rank + rot)] over the cache rows of
     ``pool`` [pages, 1, page_size, rank + rot], whose values are their leading ``rank`` columns.
     True 32-bit, or widths that the tensor-core kernel does not take: the FP32-core kernel.
-    Else the tensor-core kernel, once for the entries of at most 16 rows (decoded tokens) and
-    once for the others, each with its keys in as many slices as fill the device.
+    Else the tensor-core kernel, once for the entries of one token or at most 16 rows (16-row
+    tiles) and once for the others, each with its keys in as many slices as fill the device.
     ``padded``: the step's shape is fixed by a captured graph (this many rows): tile counts
     and slices are then bounds that depend on the shape alone.  Returns the launches."""
     width = rank + rot
@@ -149,13 +149,15 @@ def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len,
         return 1
     n_entries = kv_len.shape[0]
     if padded is not None:
-        small_tiles = n_entries if heads <= 16 else 0
+        small_tiles = n_entries * (-(-heads // 16))
         big_tiles = n_entries + (int(padded) * heads) // 64
         most_keys = 1 << 30
     else:
-        rows = (h_cu_q[1:n_entries + 1] - h_cu_q[:n_entries]) * heads
-        small_tiles = int(((rows > 0) & (rows <= 16)).sum())
-        big_tiles = int(((rows[rows > 16] + 63) // 64).sum())
+        q_lens = h_cu_q[1:n_entries + 1] - h_cu_q[:n_entries]
+        rows = q_lens * heads
+        small = (rows > 0) & ((q_lens == 1) | (rows <= 16))
+        small_tiles = int(((rows[small] + 15) // 16).sum())
+        big_tiles = int(((rows[(rows > 0) & ~small] + 63) // 64).sum())
         most_keys = int(h_kv_len[:n_entries].max())
     if scratch is None:
         scratch = lambda name, n, cols, cap: torch.empty((n, cols), dtype=torch.float32, device=q.device)
@@ -169,7 +171,8 @@ def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len,
         splits = max(1, min(64 if small else 8, ((4 if small else 1) * num_sms) // tiles, -(-most_keys // 128)))
         part_o = part_ml = None
         if splits > 1:
-            cap = (max_small * 16 * 64) if small else (num_sms + 1) * 64
+            # (with two slices or more, tiles x slices is at most the CTAs aimed at)
+            cap = 4 * num_sms * 16 if small else (num_sms + 1) * 64
             part_o = scratch("latent_part_o" + ("_s" if small else ""), tiles * splits * bm, rank, max(cap, tiles * splits * bm))
             part_ml = scratch("latent_part_ml" + ("_s" if small else ""), tiles * splits * bm, 2, max(cap, tiles * splits * bm))
         k.latent_attention_mma(q, out, pool, cu_q, kv_len, table, page_size, tiles, splits, small, heads, width,
