@@ -380,3 +380,23 @@ def test_greedy_batch_bfloat16_through_the_scheduler(name, model_folders):
             assert row[toks[i]] >= row.max() - 3e-2 * np.abs(row).max(), (i, toks[i], int(row.argmax()))
     m.runner.table.check()
     assert m.runner.table.live() == 0
+
+
+def test_command_line(model_folders):
+    """bin/crane picks the model class from config.json; sampling with a temperature runs too."""
+    import os
+    import subprocess
+    import sys
+    folder = model_folders("RA", "float32")
+    cfg, w = pr.load_folder(folder)
+    crane = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "crane")
+    cmd = [sys.executable, crane, "-m", folder, "--dtype", "fp32", "--prompt-ids", "5,6,7", "--max-new-tokens", "6",
+           "--eos-token-id", "-1", "--page-size", "16", "--num-pages", "8", "-c", "2", "--max-batched-tokens", "32",
+           "--max-seq-len", "64"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert p.stdout.strip().splitlines()[-1] == ",".join(map(str, pr.greedy_generate(cfg, w, [5, 6, 7], 6)[3:]))
+    p = subprocess.run(cmd + ["--temperature", "0.8", "--top-k", "20", "--top-p", "0.9", "--random-weights", "--seed", "3"],
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert len(p.stdout.strip().splitlines()[-1].split(",")) == 6
