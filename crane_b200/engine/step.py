@@ -85,6 +85,7 @@ class StepContext:
                                 # an attention mixer may give them to its split-KV decode kernel and
                                 # the rest to its prefill kernel
     short_prompts: bool = False     # no entry has more than 64 keys in all (whole short prompts)
+    all_single: bool = False        # every entry has exactly one token (part of a padded step's shape)
 
 
 class _MetaBuffers:
@@ -163,7 +164,10 @@ class ModelRunner:
         # Steps of single tokens are padded to a batch-size bucket (rows of no entry, entries without
         # rows) and replay that bucket's graph; with a mixer that keeps state they are padded as
         # steps with prompt portions are, to a shape of their own.
-        self._pad_with_copies = not has_state
+        # (State that only the embedding keeps, one token per request that its kernel reads and replaces
+        # for entries with rows alone, bears the bucket's padding as well.)
+        mixer_state = any(n.kind == "state" for n in self.model.cache_needs()[:len(self.spec.schedule)])
+        self._pad_with_copies = not mixer_state
         self.graph_replays = 0
         self.graph_captures = 0                    # steps that ran kernel by kernel and were recorded for their shape
         self._step_done = torch.cuda.Event()       # recorded behind every step's kernels
@@ -319,7 +323,8 @@ class ModelRunner:
             shape = ("rows", rows, self._power_of_two(n_entries, self.cap_entries),
                      self._power_of_two(wanted, rows) if wanted else 0,
                      self._power_of_two(singles, self.cap_entries) if singles else 0,
-                     1 if short_prompts else 0)
+                     1 if short_prompts else 0,
+                     1 if int(cnt.max()) == 1 else 0)     # nothing but single tokens: a decode step
             seen = self._shape_seen.get(shape, 0) + 1
             self._shape_seen[shape] = seen
             if seen >= 2:
@@ -371,6 +376,7 @@ class ModelRunner:
         ctx.graph_key = key
         ctx.single_entries = singles
         ctx.short_prompts = short_prompts
+        ctx.all_single = int(cnt.max()) == 1
         # While the device still runs the step before, the host launches this step's kernels
         # behind it at no cost, and launched one by one they ran a little faster than replayed
         # (a serving mix: 5 % per step): a graph pays when the device waits for the host.  The

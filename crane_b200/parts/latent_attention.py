@@ -122,6 +122,7 @@ class LatentAttention(Part):
             k, q_abs, o_lat, cache.k, ctx.positions, ctx.tok_entry, ctx.cu_q, ctx.kv_len, ctx.h_cu_q,
             ctx.h_kv_len, table, cache.page_size, H, r, rot, self.scale, rt.err, rt.exact,
             padded=ctx.n_tokens if shape_only else None, num_sms=rt.num_sms,
+            all_single=bool(getattr(ctx, "all_single", False)) or ctx.graph_bucket > 0,
             scratch=lambda name, rows, cols, cap: rt.ws.get(name, rows, cols, torch.float32, cap=cap),
             max_small=rt.max_decode_rows)
         o = rt.ws.get("attn_o", n, H * vd, rt.dtype)
@@ -134,14 +135,15 @@ class LatentAttention(Part):
 
 def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len, h_cu_q, h_kv_len, table,
                             page_size, heads, rank, rot, scale, err, exact, padded=None, num_sms=148,
-                            scratch=None, max_small=64) -> int:
+                            scratch=None, max_small=64, all_single=False) -> int:
     """out [N, heads * rank] = attention of q [N, heads * (rank + rot)] over the cache rows of
     ``pool`` [pages, 1, page_size, rank + rot], whose values are their leading ``rank`` columns.
     True 32-bit, or widths that the tensor-core kernel does not take: the FP32-core kernel.
     Else the tensor-core kernel, once for the entries of one token or at most 16 rows (16-row
     tiles) and once for the others, each with its keys in as many slices as fill the device.
     ``padded``: the step's shape is fixed by a captured graph (this many rows): tile counts
-    and slices are then bounds that depend on the shape alone.  Returns the launches."""
+    and slices are then bounds that depend on the shape alone (``all_single``: the shape says
+    that every entry has one token).  Returns the launches."""
     width = rank + rot
     if exact or not k.latent_attention_mma_supports(width, rank):
         k.paged_attention_simt(q, out, pool, pool, positions, tok_entry, table, page_size, heads, 1, width, 0,
@@ -150,7 +152,8 @@ def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len,
     n_entries = kv_len.shape[0]
     if padded is not None:
         small_tiles = n_entries * (-(-heads // 16))
-        big_tiles = n_entries + (int(padded) * heads) // 64
+        # (a step of nothing but single tokens, which is part of a padded step's shape, has no 64-row tiles)
+        big_tiles = 0 if all_single else n_entries + (int(padded) * heads) // 64
         most_keys = 1 << 30
     else:
         q_lens = h_cu_q[1:n_entries + 1] - h_cu_q[:n_entries]
