@@ -172,16 +172,26 @@ head_linear_mma_kernel(GemmOut<__nv_bfloat16> x, int x_cols, int x_off, int x_he
     pdl_launch_dependents();
     // the head's matrix depends on no earlier kernel
     const __nv_bfloat16* wh = w + (long long)h * n_in * n_out;
-    for (int r = warp; r < n_in; r += 4)
-        for (int c = lane; c < (n_out >> 3); c += 32) hl_cp16(w_s + r * ldw + c * 8, wh + (long long)r * n_out + c * 8, true);
+    {
+        const int n16w = (n_out + 15) >> 4;
+        const int zper = FEW ? (n16w + (int)gridDim.z - 1) / (int)gridDim.z : n16w;
+        const int c_lo = FEW ? (int)blockIdx.z * zper * 2 : 0;
+        const int c_hi = min(n_out >> 3, c_lo + zper * 2);
+        for (int r = warp; r < n_in; r += 4)
+            for (int c = c_lo + lane; c < c_hi; c += 32) hl_cp16(w_s + r * ldw + c * 8, wh + (long long)r * n_out + c * 8, true);
+    }
     pdl_wait();
     // At most 16 tokens in the tile (a decode step): the four warps share the one block of 16 rows and
     // take a quarter of the output columns each, instead of a block of rows each.
     constexpr bool few = FEW;                                       // (the launch has 16 tokens at most)
     const int wrow = few ? 0 : warp * 16;
     const int n16 = (n_out + 15) >> 4;                              // pairs of 8 output columns
-    const int per = few ? (n16 + 3) >> 2 : n16;
-    const int n2_lo = few ? warp * per : 0, n2_hi = min(n16, n2_lo + per);
+    // (and the few-token form spreads the columns over gridDim.z CTAs first, each of which fetches its
+    // columns of the matrix alone)
+    const int cta_per = few ? (n16 + (int)gridDim.z - 1) / (int)gridDim.z : n16;
+    const int cta_lo = few ? (int)blockIdx.z * cta_per : 0, cta_hi = min(n16, cta_lo + cta_per);
+    const int per = few ? (cta_hi - cta_lo + 3) >> 2 : n16;
+    const int n2_lo = few ? cta_lo + warp * per : 0, n2_hi = few ? min(cta_hi, n2_lo + per) : n16;
     for (int r = warp; r < (few ? 16 : HM_TT); r += 4) {
         const bool ok = t0 + r < n_tokens;
         const long long at = ok ? (long long)(t0 + r) * x_cols + x_off + (long long)h * x_head : 0;
@@ -281,7 +291,8 @@ CRANE_API int crane_head_linear(int dtype, const void* x, const float* x_parts, 
         }
         GemmOut<__nv_bfloat16> gx{(const __nv_bfloat16*)x, x_parts, x_n, x_stride};
         GemmOut<__nv_bfloat16> gg{(const __nv_bfloat16*)gate, g_parts, g_n, g_stride};
-        return crane_launch(kern, dim3((n_tokens + HM_TT - 1) / HM_TT, heads), dim3(128), sm, st, gx, x_cols, x_off,
+        const int zs = n_tokens <= 16 ? ((n_out + 15) / 16 < 4 ? (n_out + 15) / 16 : 4) : 1;
+        return crane_launch(kern, dim3((n_tokens + HM_TT - 1) / HM_TT, heads, zs), dim3(128), sm, st, gx, x_cols, x_off,
                             x_head, (const __nv_bfloat16*)w, n_in, n_out, gg,
                             (gate != nullptr || g_parts != nullptr) ? 1 : 0, g_cols, g_off, tok_entry,
                             (__nv_bfloat16*)out, out_pitch, out_head, n_tokens);
