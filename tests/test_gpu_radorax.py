@@ -285,7 +285,7 @@ def _latent_reference(q, rows, pos, rank, scale):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rank, rot, heads, ps", [(32, 8, 4, 16), (72, 4, 5, 8), (96, 16, 6, 64), (128, 32, 8, 64)])
+@pytest.mark.parametrize("rank, rot, heads, ps", [(32, 8, 4, 16), (72, 4, 5, 8), (80, 16, 7, 32), (128, 32, 8, 64), (176, 48, 20, 16)])
 def test_attention_in_the_latent_space_with_planted_keys(K, dtype, rank, rot, heads, ps):
     """A prompt portion and single tokens over long cached contexts; for some queries one key
     (far back, first of all, at a page's last and first place, the newest) is made to stand out
