@@ -113,14 +113,16 @@ class Runtime:
             self.kernels.gemm_simt(x, w, bias, out)
             self.launches += 1
             return out
-        # A many-token product launched straight behind another product (the two branches of a
+        # A product launched straight behind another product (the two branches of a
         # parallel block: output projection, then the feed-forward's first matrix) does not start
         # before that one has finished.  With programmatic dependent launch its CTAs could come to
         # rest on an SM beside a CTA of the running product that has announced its dependents but
         # not yet taken its tensor memory, take all of it and wait for that product: neither would
         # end.  (Seen as a prefill of 2,048 tokens that never finished; sequences with a kernel of
         # another kind between two products, which is all that Hunyuan Dense has, are not affected.)
-        serial = M > self.split_rows and self.launches == self._after_product and self.kernels.pdl_default
+        # (Few-token products take little tensor memory and were not seen to do this, but nothing rules
+        # it out for them either, and the edge is one of eleven in a layer: they are launched the same way.)
+        serial = self.launches == self._after_product and self.kernels.pdl_default
         if serial:
             self.kernels.lib.crane_set_pdl(0)
         try:
