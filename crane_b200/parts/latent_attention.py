@@ -123,8 +123,7 @@ class LatentAttention(Part):
             ctx.h_kv_len, table, cache.page_size, H, r, rot, self.scale, rt.err, rt.exact,
             padded=ctx.n_tokens if shape_only else None, num_sms=rt.num_sms,
             all_single=bool(getattr(ctx, "all_single", False)) or ctx.graph_bucket > 0,
-            scratch=lambda name, rows, cols, cap: rt.ws.get(name, rows, cols, torch.float32, cap=cap),
-            max_small=rt.max_decode_rows)
+            scratch=lambda name, rows, cols, cap: rt.ws.get(name, rows, cols, torch.float32, cap=cap))
         o = rt.ws.get("attn_o", n, H * vd, rt.dtype)
         k.head_linear(o_lat, H * r, 0, r, self.uv_t, r, vd, o, H * vd, vd, H, tok_entry=ctx.tok_entry,
                       gate=proj if self.gated else None, g_cols=self.cols, g_off=self.g_off)
@@ -135,7 +134,7 @@ class LatentAttention(Part):
 
 def latent_attention_kernel(k, q, out, pool, positions, tok_entry, cu_q, kv_len, h_cu_q, h_kv_len, table,
                             page_size, heads, rank, rot, scale, err, exact, padded=None, num_sms=148,
-                            scratch=None, max_small=64, all_single=False) -> int:
+                            scratch=None, all_single=False) -> int:
     """out [N, heads * rank] = attention of q [N, heads * (rank + rot)] over the cache rows of
     ``pool`` [pages, 1, page_size, rank + rot], whose values are their leading ``rank`` columns.
     True 32-bit, or widths that the tensor-core kernel does not take: the FP32-core kernel.
