@@ -282,11 +282,21 @@ CRANE_API int crane_head_linear(int dtype, const void* x, const float* x_parts, 
                          ((uintptr_t)x | (uintptr_t)w) % 16 == 0 && ((uintptr_t)out | (uintptr_t)gate) % 4 == 0;
     if (dtype == 1 && aligned && n_in % 16 == 0 && n_out % 8 == 0 && n_in <= 256 && n_out <= 256) {
         const size_t sm = ((size_t)HM_TT * (n_in + 8) + (size_t)n_in * (n_out + 8)) * sizeof(__nv_bfloat16);
-        auto kern = n_tokens <= 16 ? head_linear_mma_kernel<16, 32, true> : head_linear_mma_kernel<16, 32, false>;
+        // (the column blocks are unrolled: an instantiation per bound keeps the code of the common widths short)
+        const bool few_tokens = n_tokens <= 16;
+        const int n8 = n_out >> 3;
+        auto kern = n8 <= 16 ? (few_tokens ? head_linear_mma_kernel<16, 16, true> : head_linear_mma_kernel<16, 16, false>)
+                  : n8 <= 24 ? (few_tokens ? head_linear_mma_kernel<16, 24, true> : head_linear_mma_kernel<16, 24, false>)
+                             : (few_tokens ? head_linear_mma_kernel<16, 32, true> : head_linear_mma_kernel<16, 32, false>);
         static bool attr_set = false;
         if (!attr_set) {
-            cudaFuncSetAttribute(head_linear_mma_kernel<16, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            cudaFuncSetAttribute(head_linear_mma_kernel<16, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            const int most = 200 * 1024;
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 24, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 24, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            cudaFuncSetAttribute(head_linear_mma_kernel<16, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
             attr_set = true;
         }
         GemmOut<__nv_bfloat16> gx{(const __nv_bfloat16*)x, x_parts, x_n, x_stride};
