@@ -1,8 +1,9 @@
 """Typed configurations and the architecture registry."""
 from .hunyuan_dense import (ALIASES, ARCHITECTURE, ConfigError, HunyuanDenseConfig, RopeScaling,
                             build_spec, read_config_json)
-from . import radorax
+from . import radorax, vodelix
 from .radorax import RadoraxConfig
+from .vodelix import VodelixConfig
 from .registry import (Architecture, UnknownArchitecture, register_architecture, registered,
                        resolve)
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleStep
@@ -10,7 +11,8 @@ from .engine_config import EngineConfig, parse_memory_limit
 
 register_architecture(ARCHITECTURE, HunyuanDenseConfig.from_dict, build_spec, ALIASES)
 register_architecture(radorax.ARCHITECTURE, RadoraxConfig.from_dict, radorax.build_spec, radorax.ALIASES)
+register_architecture(vodelix.ARCHITECTURE, VodelixConfig.from_dict, vodelix.build_spec, vodelix.ALIASES)
 
-__all__ = ["ConfigError", "HunyuanDenseConfig", "RadoraxConfig", "RopeScaling", "read_config_json", "Architecture",
+__all__ = ["ConfigError", "HunyuanDenseConfig", "RadoraxConfig", "VodelixConfig", "RopeScaling", "read_config_json", "Architecture",
            "UnknownArchitecture", "register_architecture", "registered", "resolve", "LayerSpec",
            "ModelSpec", "PartSpec", "ScheduleStep", "EngineConfig", "parse_memory_limit"]

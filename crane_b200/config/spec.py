@@ -37,6 +37,10 @@ class ScheduleStep:
     step that reads another's cache writes none."""
     layer: int
     cache_of: Optional[int] = None
+    # what happens to the stream before the layer runs: arguments for the model's ``entry`` part
+    # (``ModelSpec.entry``), e.g. {"row": 1, "add_embedding": True} where a pass over repeated
+    # layers begins; None: nothing
+    enter: Optional[Dict[str, Any]] = None
 
     def cache_step(self, own_place: int) -> int:
         return own_place if self.cache_of is None else self.cache_of
@@ -53,6 +57,8 @@ class ModelSpec:
     schedule: List[ScheduleStep]
     final_norm: PartSpec
     head: PartSpec
+    # the part that a schedule step's ``enter`` calls (kind "entry"), if any step has one
+    entry: Optional[PartSpec] = None
     eos_token_ids: List[int] = field(default_factory=list)
     # tensors that a checkpoint of this architecture may hold and the model
     # never reads (name -> reason); they are not reported as unexpected

@@ -6,7 +6,8 @@
 // One warp per (token, query head): the token at position p of
 // request e attends the keys of positions max(0, p - window + 1) .. p of the
 // same request, found through the request's block table.  Scores, softmax
-// statistics and the weighted sum are float whatever the storage type.
+// statistics and the weighted sum are float whatever the storage type.  `sink`: the
+// softmax has one more candidate of score 0 and no value (p_j = exp(s_j) / (1 + sum exp(s))).
 //
 // scores = q k^T / sqrt(d), causal j <= p, softmax over the last dimension,
 // query head h reads kv head h / (nq / nkv):
@@ -25,7 +26,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
                             const int* __restrict__ positions, const int* __restrict__ tok_entry,
                             const int* __restrict__ block_table, int max_blocks, int num_pages,
                             int page_size, int n_tokens, int nq, int nkv, int d, int dv,
-                            int v_stride, int window, float scale, int* err) {
+                            int v_stride, int window, float scale, int sink, int* err) {
     extern __shared__ float q_all[];              // [WARPS][d]
     float* q_s = q_all + (threadIdx.x >> 5) * d;
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,6 +87,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
         }
     }
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
+    // a sink: one more candidate of score 0 that has no value, so it only adds exp(0 - m) to the sum
+    if (sink) l += expf(-m);
     const float inv = l > 0.f ? 1.f / l : 0.f;
     T* op = out + ((long long)t * nq + h) * dv;
 #pragma unroll
@@ -101,7 +104,7 @@ CRANE_API int crane_paged_attention_simt(int dtype, const void* q, void* out, co
                                          const int* tok_entry, const int* block_table,
                                          int max_blocks, int num_pages, int page_size,
                                          int n_tokens, int nq, int nkv, int d, int dv,
-                                         int v_stride, int window, float scale, int* err,
+                                         int v_stride, int window, float scale, int sink, int* err,
                                          cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (d > MAXD || d <= 0 || dv > MAXDV || dv <= 0 || v_stride < dv || nkv <= 0 || nq % nkv != 0)
@@ -113,11 +116,11 @@ CRANE_API int crane_paged_attention_simt(int dtype, const void* q, void* out, co
         paged_attention_simt_kernel<float><<<blocks, WARPS * 32, smem, st>>>(
             (const float*)q, (float*)out, (const float*)k_pool, (const float*)v_pool, positions,
             tok_entry, block_table, max_blocks, num_pages, page_size, n_tokens, nq, nkv, d, dv,
-            v_stride, window, scale, err);
+            v_stride, window, scale, sink, err);
     else
         paged_attention_simt_kernel<__nv_bfloat16><<<blocks, WARPS * 32, smem, st>>>(
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, tok_entry, block_table, max_blocks, num_pages,
-            page_size, n_tokens, nq, nkv, d, dv, v_stride, window, scale, err);
+            page_size, n_tokens, nq, nkv, d, dv, v_stride, window, scale, sink, err);
     return crane_launch_status();
 }

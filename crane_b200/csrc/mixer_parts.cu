@@ -1,0 +1,327 @@
+// Kernels of two mixers.
+//
+// 1. Attention whose queries and keys are RMS-normed over their whole projections (all heads at
+//    once) and not rotated: `projection_norm_cache` norms q and k, writes q for the attention kernel
+//    and the token's key and value rows into the pages.  Key and value rows may be stored wider than
+//    they are (zero-filled), so that kernels written for one head size serve both.
+//
+// 2. The generalized delta rule, a linear recurrence with one matrix state S [dk, dv] per head:
+//        S <- diag(w) S - (a * u) (u^T S) + k v^T,     o = S^T r
+//    w the decay per key channel, a the removal rate, u the key scaled to unit length; both
+//    corrections read the state before the token.  `delta_rule_prep` forms w, a * u and u of every
+//    token in 32-bit; `delta_rule_scan` walks each request's tokens in order with the state of a head
+//    spread over the threads of a CTA (a thread owns a column of S: columns do not talk to one
+//    another), then norms each head's read-out, gates it and writes it for the output projection.
+//    The state lives in 32-bit in the request's slot between steps.
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------ projection norm + cache write
+// qkv row: [q (nq * d) | k (nkv * d) | v (nkv * dv)].  One CTA per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+projection_norm_cache_kernel(GemmOut<T> qkv, int cols, const int* __restrict__ positions,
+                             const int* __restrict__ tok_entry, const int* __restrict__ block_table,
+                             int max_blocks, int num_pages, int page_size, const float* __restrict__ qw,
+                             const float* __restrict__ kw, float eps, T* __restrict__ q_out,
+                             T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int dv,
+                             int d_store, int dv_store, int* err) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int e = tok_entry[t];
+    if (e < 0) return;
+    const long long base = (long long)t * cols;
+    const int nqd = nq * d, nkd = nkv * d, nvd = nkv * dv;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < nqd; c += blockDim.x) { const float v = qkv.load(base + c); sq += v * v; }
+    for (int c = threadIdx.x; c < nkd; c += blockDim.x) { const float v = qkv.load(base + nqd + c); sk += v * v; }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    const float rq = qw != nullptr ? rsqrtf(sq / (float)nqd + eps) : 1.f;
+    const float rk = kw != nullptr ? rsqrtf(sk / (float)nkd + eps) : 1.f;
+    // queries, heads d_store apart
+    for (int c = threadIdx.x; c < nq * d_store; c += blockDim.x) {
+        const int h = c / d_store, i = c % d_store;
+        float v = 0.f;
+        if (i < d) v = qkv.load(base + h * d + i) * rq * (qw != nullptr ? qw[h * d + i] : 1.f);
+        q_out[(long long)t * nq * d_store + c] = from_f32<T>(v);
+    }
+    const int pos = positions[t];
+    const int blk = pos / page_size;
+    const int page = blk < max_blocks ? block_table[(long long)e * max_blocks + blk] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
+        return;
+    }
+    const int slot = pos % page_size;
+    for (int c = threadIdx.x; c < nkv * d_store; c += blockDim.x) {
+        const int g = c / d_store, i = c % d_store;
+        float v = 0.f;
+        if (i < d) v = qkv.load(base + nqd + g * d + i) * rk * (kw != nullptr ? kw[g * d + i] : 1.f);
+        k_pool[(((long long)page * nkv + g) * page_size + slot) * d_store + i] = from_f32<T>(v);
+    }
+    for (int c = threadIdx.x; c < nkv * dv_store; c += blockDim.x) {
+        const int g = c / dv_store, i = c % dv_store;
+        const float v = i < dv ? qkv.load(base + nqd + nkd + g * dv + i) : 0.f;
+        v_pool[(((long long)page * nkv + g) * page_size + slot) * dv_store + i] = from_f32<T>(v);
+    }
+    (void)nvd;
+}
+
+// ------------------------------------------------------ delta rule: per-token inputs
+// proj row: [r | k | v | g | a | low] with r, k, v, g, a of heads * d columns and `rank` columns of
+// the decay's inner product.  aux row (float): [w | a * u | u], each heads * d.
+//   w = exp(-decay_scale * sigmoid(sum_j w2[c][j] tanh(low[j]) + w0[c]))
+//   a = sigmoid(a_pre + ab[c]);  u = k / sqrt(sum over the head of k^2 + key_eps)
+// One CTA per token; a warp per head for the key's length.
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_rule_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_entry, const T* __restrict__ w2,
+                       const float* __restrict__ w0, const float* __restrict__ ab, float* __restrict__ aux,
+                       int heads, int d, int rank, float decay_scale, float key_eps) {
+    extern __shared__ float sm[];          // [rank] tanh(low), [heads] 1 / |k|
+    float* th = sm;
+    float* inv_len = sm + rank;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (tok_entry[t] < 0) return;
+    const int hd = heads * d;
+    const long long base = (long long)t * cols;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(proj.load(base + 5 * hd + j));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < heads; h += nwarps) {
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) { const float kv = proj.load(base + hd + h * d + i); ss += kv * kv; }
+        ss = warp_sum(ss);
+        if (lane == 0) inv_len[h] = rsqrtf(ss + key_eps);
+    }
+    __syncthreads();
+    float* out = aux + (long long)t * 3 * hd;
+    for (int c = threadIdx.x; c < hd; c += blockDim.x) {
+        float low = w0[c];
+        const T* wr = w2 + (long long)c * rank;
+        for (int j = 0; j < rank; ++j) low = fmaf(to_f32(wr[j]), th[j], low);
+        const float w = expf(-decay_scale / (1.f + expf(-low)));
+        const float a = 1.f / (1.f + expf(-(proj.load(base + 4 * hd + c) + ab[c])));
+        const float u = proj.load(base + hd + c) * inv_len[c / d];
+        out[c] = w;
+        out[hd + c] = a * u;
+        out[2 * hd + c] = u;
+    }
+}
+
+// ------------------------------------------------------ delta rule: the recurrence
+// grid (entries, heads); thread j < d owns column j of the head's state.  DK > 0: the column lives in
+// registers (d == DK); DK == 0: in shared memory (any d that fits).  Tokens come in tiles of TT whose
+// per-token vectors (r, k, w, a u, u over the key channels, v and the gate over the columns) all threads
+// load together.  After a tile, a warp per token norms the head's read-out (RMS over the columns),
+// multiplies by the norm's weight and sigmoid(gate) and writes T for the output projection.
+constexpr int TT = 16;
+
+template <typename T, int DK>
+__global__ void __launch_bounds__(256)
+delta_rule_scan_kernel(GemmOut<T> proj, int cols, const float* __restrict__ aux, const int* __restrict__ cu_q,
+                       const int* __restrict__ kv_len, const int* __restrict__ slots, int n_slots,
+                       float* __restrict__ state, const float* __restrict__ norm_w, float norm_eps,
+                       T* __restrict__ out, int heads, int d, int* err) {
+    extern __shared__ float sm[];
+    // layout: vec [TT][5][d] (r, k, w, au, u), val [TT][d] (v), gate [TT][d], o [TT][d], then the state (DK == 0)
+    float* vec = sm;
+    float* val = vec + TT * 5 * d;
+    float* gat = val + TT * d;
+    float* o_s = gat + TT * d;
+    float* S_s = o_s + TT * d;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.x, h = blockIdx.y;
+    const int first = cu_q[e], n = cu_q[e + 1] - first;
+    if (n <= 0) return;                                  // an entry that pads the step: no slot is touched
+    int slot = slots[e];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_SLOT_RANGE);
+        return;
+    }
+    const int j = threadIdx.x;
+    const bool own = j < d;
+    const int hd = heads * d;
+    float* S_g = state + ((long long)slot * heads + h) * d * d;
+    const bool fresh = kv_len[e] - n == 0;               // the request's first tokens: the state starts at zero
+    float S[DK > 0 ? DK : 1];
+    if (own) {
+        if (DK > 0) {
+#pragma unroll
+            for (int i = 0; i < DK; ++i) S[i] = fresh ? 0.f : S_g[i * d + j];
+        } else {
+            for (int i = 0; i < d; ++i) S_s[i * d + j] = fresh ? 0.f : S_g[i * d + j];
+        }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int t0 = 0; t0 < n; t0 += TT) {
+        const int nt = min(TT, n - t0);
+        __syncthreads();                                 // the tile before has been read out
+        for (int idx = threadIdx.x; idx < nt * d; idx += blockDim.x) {
+            const int tt = idx / d, c = idx % d;
+            const long long row = (long long)(first + t0 + tt);
+            const long long pb = row * cols + h * d + c;
+            const float* ax = aux + row * 3 * hd + h * d + c;
+            float* v5 = vec + (tt * 5) * d + c;
+            v5[0] = proj.load(pb);                       // r
+            v5[d] = proj.load(pb + hd);                  // k
+            v5[2 * d] = ax[0];                           // w
+            v5[3 * d] = ax[hd];                          // a u
+            v5[4 * d] = ax[2 * hd];                      // u
+            val[tt * d + c] = proj.load(pb + 2 * hd);    // v
+            gat[tt * d + c] = proj.load(pb + 3 * hd);    // gate, before its sigmoid
+        }
+        __syncthreads();
+        if (own) {
+            for (int tt = 0; tt < nt; ++tt) {
+                const float* r = vec + (tt * 5) * d;
+                const float *k = r + d, *w = r + 2 * d, *au = r + 3 * d, *u = r + 4 * d;
+                const float v = val[tt * d + j];
+                float dot0 = 0.f, dot1 = 0.f, dot2 = 0.f, dot3 = 0.f;
+                if (DK > 0) {
+#pragma unroll
+                    for (int i = 0; i < DK; i += 4) {
+                        dot0 = fmaf(u[i], S[i], dot0);
+                        dot1 = fmaf(u[i + 1], S[i + 1], dot1);
+                        dot2 = fmaf(u[i + 2], S[i + 2], dot2);
+                        dot3 = fmaf(u[i + 3], S[i + 3], dot3);
+                    }
+                } else {
+                    for (int i = 0; i < d; ++i) dot0 = fmaf(u[i], S_s[i * d + j], dot0);
+                }
+                const float dot = (dot0 + dot1) + (dot2 + dot3);
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+                if (DK > 0) {
+#pragma unroll
+                    for (int i = 0; i < DK; i += 4) {
+                        S[i] = fmaf(w[i], S[i], fmaf(-au[i], dot, k[i] * v));
+                        S[i + 1] = fmaf(w[i + 1], S[i + 1], fmaf(-au[i + 1], dot, k[i + 1] * v));
+                        S[i + 2] = fmaf(w[i + 2], S[i + 2], fmaf(-au[i + 2], dot, k[i + 2] * v));
+                        S[i + 3] = fmaf(w[i + 3], S[i + 3], fmaf(-au[i + 3], dot, k[i + 3] * v));
+                        o0 = fmaf(r[i], S[i], o0);
+                        o1 = fmaf(r[i + 1], S[i + 1], o1);
+                        o2 = fmaf(r[i + 2], S[i + 2], o2);
+                        o3 = fmaf(r[i + 3], S[i + 3], o3);
+                    }
+                } else {
+                    for (int i = 0; i < d; ++i) {
+                        const float s = fmaf(w[i], S_s[i * d + j], fmaf(-au[i], dot, k[i] * v));
+                        S_s[i * d + j] = s;
+                        o0 = fmaf(r[i], s, o0);
+                    }
+                }
+                o_s[tt * d + j] = (o0 + o1) + (o2 + o3);
+            }
+        }
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += nwarps) {
+            float ss = 0.f;
+            for (int c = lane; c < d; c += 32) { const float v = o_s[tt * d + c]; ss += v * v; }
+            ss = warp_sum(ss);
+            const float rs = rsqrtf(ss / (float)d + norm_eps);
+            T* op = out + (long long)(first + t0 + tt) * hd + h * d;
+            for (int c = lane; c < d; c += 32) {
+                const float g = 1.f / (1.f + expf(-gat[tt * d + c]));
+                op[c] = from_f32<T>(o_s[tt * d + c] * rs * norm_w[h * d + c] * g);
+            }
+        }
+    }
+    if (own) {
+        if (DK > 0) {
+#pragma unroll
+            for (int i = 0; i < DK; ++i) S_g[i * d + j] = S[i];
+        } else {
+            for (int i = 0; i < d; ++i) S_g[i * d + j] = S_s[i * d + j];
+        }
+    }
+}
+
+template <typename T, int DK>
+int launch_scan(GemmOut<T> proj, int cols, const float* aux, const int* cu_q, const int* kv_len, const int* slots,
+                int n_slots, float* state, const float* norm_w, float norm_eps, T* out, int n_entries, int heads,
+                int d, int* err, cudaStream_t st) {
+    size_t smem = (size_t)(TT * 8 * d) * sizeof(float);
+    if (DK == 0) smem += (size_t)d * d * sizeof(float);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(delta_rule_scan_kernel<T, DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int threads = (d + 31) / 32 * 32;
+    return crane_launch(delta_rule_scan_kernel<T, DK>, dim3(n_entries, heads), dim3(threads < 64 ? 64 : threads), smem,
+                        st, proj, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out, heads, d, err);
+}
+
+template <typename T>
+int scan_dispatch(GemmOut<T> g, int cols, const float* aux, const int* cu_q, const int* kv_len, const int* slots,
+                  int n_slots, float* state, const float* norm_w, float norm_eps, T* out, int n_entries, int heads,
+                  int d, int* err, cudaStream_t st) {
+#define SCAN(DK) return launch_scan<T, DK>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out, \
+                                           n_entries, heads, d, err, st)
+    switch (d) {
+        case 16: SCAN(16);
+        case 32: SCAN(32);
+        case 64: SCAN(64);
+        case 128: SCAN(128);
+        default: SCAN(0);
+    }
+#undef SCAN
+}
+
+}  // namespace
+
+CRANE_API int crane_projection_norm_cache(int dtype, const void* qkv, const float* qkv_parts, int n_parts,
+                                          long long part_stride, int cols, const int* positions,
+                                          const int* tok_entry, const int* block_table, int max_blocks,
+                                          int num_pages, int page_size, const float* qw, const float* kw,
+                                          float eps, void* q_out, void* k_pool, void* v_pool, int n_tokens,
+                                          int nq, int nkv, int d, int dv, int d_store, int dv_store, int* err,
+                                          cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (d_store < d || dv_store < dv) return (int)cudaErrorInvalidValue;
+    DISPATCH_T(dtype, {
+        GemmOut<T> g{(const T*)qkv, qkv_parts, n_parts, part_stride};
+        return crane_launch(projection_norm_cache_kernel<T>, dim3(n_tokens), dim3(256), 0, st, g, cols, positions,
+                            tok_entry, block_table, max_blocks, num_pages, page_size, qw, kw, eps, (T*)q_out,
+                            (T*)k_pool, (T*)v_pool, nq, nkv, d, dv, d_store, dv_store, err);
+    });
+}
+
+CRANE_API int crane_delta_rule_prep(int dtype, const void* proj, const float* proj_parts, int n_parts,
+                                    long long part_stride, int cols, const int* tok_entry, const void* w2,
+                                    const float* w0, const float* ab, float* aux, int n_tokens, int heads,
+                                    int d, int rank, float decay_scale, float key_eps, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    const size_t smem = (size_t)(rank + heads) * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    DISPATCH_T(dtype, {
+        GemmOut<T> g{(const T*)proj, proj_parts, n_parts, part_stride};
+        return crane_launch(delta_rule_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, st, g, cols, tok_entry,
+                            (const T*)w2, w0, ab, aux, heads, d, rank, decay_scale, key_eps);
+    });
+}
+
+// The widest head the recurrence takes: its state and a tile of vectors must fit shared memory.
+CRANE_API int crane_delta_rule_max_dim() {
+    int d = 16;
+    while ((size_t)(TT * 8 * (d + 1) + (d + 1) * (d + 1)) * sizeof(float) <= 227 * 1024) ++d;
+    return d;
+}
+
+CRANE_API int crane_delta_rule_scan(int dtype, const void* proj, const float* proj_parts, int n_parts,
+                                    long long part_stride, int cols, const float* aux, const int* cu_q,
+                                    const int* kv_len, const int* slots, int n_slots, float* state,
+                                    const float* norm_w, float norm_eps, void* out, int n_entries, int heads,
+                                    int d, int* err, cudaStream_t st) {
+    if (n_entries <= 0) return 0;
+    if (d <= 0 || d > 1024) return (int)cudaErrorInvalidValue;
+    DISPATCH_T(dtype, {
+        GemmOut<T> g{(const T*)proj, proj_parts, n_parts, part_stride};
+        return scan_dispatch<T>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, (T*)out,
+                                n_entries, heads, d, err, st);
+    });
+}

@@ -28,7 +28,7 @@ _SIGNATURES = {
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
     "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, I, L, I, P, L, P, P],
     "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
-    "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_paged_prefill_attention_supports": [I, I, I],
@@ -44,6 +44,15 @@ _SIGNATURES = {
     "crane_head_linear": [I, P, P, I, L, I, I, I, P, I, I, P, P, I, L, I, I, P, P, I, I, I, I, P],
     "crane_latent_attention_mma_supports": [I, I],
     "crane_latent_attention_mma": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "crane_embed_sinusoid": [I, P, P, P, P, P, P, I, I, I, P, I, P, P],
+    "crane_stream_enter": [P, P, P, I, I, P],
+    "crane_add_normed_norm": [I, P, P, P, I, L, P, P, P, P, I, I, F, F, P],
+    "crane_token_gate": [I, P, P, I, L, P, P, I, I, I, P, I, I, P, I, P, P],
+    "crane_ffn_activation": [I, P, P, I, L, P, I, I, I, P, I, I, I, P],
+    "crane_route_topk": [P, P, P, P, I, I, I, P],
+    "crane_projection_norm_cache": [I, P, P, I, L, I, P, P, P, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I, P, P],
+    "crane_delta_rule_prep": [I, P, P, I, L, I, P, P, P, P, P, I, I, I, I, F, F, P],
+    "crane_delta_rule_scan": [I, P, P, I, L, I, P, P, P, P, I, P, P, F, P, I, I, I, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -272,6 +281,100 @@ class Kernels:
             kv_len.shape[0], int(tiles), int(splits), 1 if small else 0, heads, dk, dv, float(scale),
             err.data_ptr(), self._stream(q)), "latent_attention_mma")
 
+    # ---- the stream of layers that norm what they add, routed feed-forwards ----
+    def embed_sinusoid(self, tokens, positions, table, freq, x, keep, err, deferred=None) -> None:
+        """x[t] = table[token] + the sinusoid of the position (``freq`` float64 [ceil(hidden / 2)]:
+        column 2i gets sin(p freq[i]), 2i + 1 the cosine); ``keep``: a second copy of the rows."""
+        n, hidden = x.shape
+        self._check(self.lib.crane_embed_sinusoid(
+            _dt(table.dtype), tokens.data_ptr(), positions.data_ptr(), table.data_ptr(), freq.data_ptr(),
+            x.data_ptr(), _ptr(keep), n, hidden, table.shape[0], _ptr(deferred),
+            deferred.numel() if deferred is not None else 0, err.data_ptr(), self._stream(x)), "embed_sinusoid")
+
+    def stream_enter(self, x, kept, vec) -> None:
+        """x += kept (float rows like x, or None) + vec (float [hidden])."""
+        self._check(self.lib.crane_stream_enter(x.data_ptr(), _ptr(kept), vec.data_ptr(), x.shape[0], x.shape[1],
+                                                self._stream(x)), "stream_enter")
+
+    def add_normed_norm(self, x, delta: Act, w_delta, eps_delta: float, w_out=None, eps_out: float = 0.0,
+                        out=None, raw=None) -> None:
+        """x += delta / rms(delta) * w_delta; then, if given, out = x / rms(x) * w_out and
+        raw = x in the model dtype.  rms(v) = sqrt(mean(v^2) + eps)."""
+        whole, parts, n_parts, stride = _split(delta)
+        dt = out.dtype if out is not None else raw.dtype if raw is not None else (
+            delta.dtype if not isinstance(delta, Partials) else torch.bfloat16)
+        self._check(self.lib.crane_add_normed_norm(
+            _dt(dt), x.data_ptr(), whole, parts, n_parts, stride, w_delta.data_ptr(), _ptr(w_out), _ptr(out),
+            _ptr(raw), x.shape[0], x.shape[1], float(eps_delta), float(eps_out), self._stream(x)), "add_normed_norm")
+
+    def token_gate(self, z: Act, tokens, side, offset: int, out, err, deferred=None) -> None:
+        """out[t] = gelu_tanh(z[t]) * side[token[t], offset : offset + dim]."""
+        whole, parts, n_parts, stride = _split(z)
+        n, dim = out.shape
+        self._check(self.lib.crane_token_gate(
+            _dt(out.dtype), whole, parts, n_parts, stride, tokens.data_ptr(), side.data_ptr(), side.shape[1],
+            int(offset), dim, out.data_ptr(), n, side.shape[0], _ptr(deferred),
+            deferred.numel() if deferred is not None else 0, err.data_ptr(), self._stream(out)), "token_gate")
+
+    ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2}
+
+    def ffn_activation(self, up: Act, out, kind: str, route=None, per_expert: int = 0, routed_cols: int = 0) -> None:
+        """out = act(up), times ``route[t, c // per_expert]`` (float [rows, experts]) for the leading
+        ``routed_cols`` columns if routing weights are given."""
+        whole, parts, n_parts, stride = _split(up)
+        self._check(self.lib.crane_ffn_activation(
+            _dt(out.dtype), whole, parts, n_parts, stride, out.data_ptr(), out.shape[0], out.shape[1],
+            self.ACTIVATIONS[kind], _ptr(route), route.shape[1] if route is not None else 0, int(per_expert),
+            int(routed_cols), self._stream(out)), "ffn_activation")
+
+    def route_topk(self, logits, route, idx, wt) -> None:
+        """Per row of float ``logits`` [n, experts]: the ``top`` (= idx.shape[1]) largest, softmax over
+        them; ``route`` [n, experts] gets the weights (zero elsewhere), ``idx`` / ``wt`` the lists."""
+        assert logits.dtype == torch.float32 and logits.is_contiguous()
+        self._check(self.lib.crane_route_topk(logits.data_ptr(), route.data_ptr(), idx.data_ptr(), wt.data_ptr(),
+                                              logits.shape[0], logits.shape[1], idx.shape[1],
+                                              self._stream(logits)), "route_topk")
+
+    def projection_norm_cache(self, qkv: Act, cols, positions, tok_entry, block_table, page_size, q_norm_w,
+                              k_norm_w, eps, q_out, k_pool, v_pool, nq, nkv, d, dv, err) -> None:
+        """Rows [q | k | v] of a merged projection: q and k RMS-normed over all their heads at once
+        (weights [nq d], [nkv d] or None), q written to ``q_out`` [n, nq, D], k and v into the
+        token's place in the pools [pages, nkv, page_size, D / Dv], zero-filled where the pools'
+        rows are wider than d / dv."""
+        whole, parts, n_parts, stride = _split(qkv)
+        self._check(self.lib.crane_projection_norm_cache(
+            _dt(q_out.dtype), whole, parts, n_parts, stride, int(cols), positions.data_ptr(), tok_entry.data_ptr(),
+            block_table.data_ptr(), block_table.shape[1], k_pool.shape[0], page_size, _ptr(q_norm_w),
+            _ptr(k_norm_w), float(eps), q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), q_out.shape[0],
+            nq, nkv, d, dv, k_pool.shape[3], v_pool.shape[3], err.data_ptr(), self._stream(q_out)),
+            "projection_norm_cache")
+
+    def delta_rule_max_dim(self) -> int:
+        self.lib.crane_delta_rule_max_dim.restype = c_int
+        return int(self.lib.crane_delta_rule_max_dim())
+
+    def delta_rule_prep(self, proj: Act, cols, tok_entry, w2, w0, ab, aux, heads, d, decay_scale, key_eps,
+                        dtype) -> None:
+        """aux [n, 3, heads d] (float) = decay, removal rate x unit key, unit key of every token, from
+        rows [r | k | v | g | a | low (rank)] of the merged projection."""
+        whole, parts, n_parts, stride = _split(proj)
+        self._check(self.lib.crane_delta_rule_prep(
+            _dt(dtype), whole, parts, n_parts, stride, int(cols), tok_entry.data_ptr(), w2.data_ptr(), w0.data_ptr(),
+            ab.data_ptr(), aux.data_ptr(), aux.shape[0], heads, d, w2.shape[1], float(decay_scale), float(key_eps),
+            self._stream(aux)), "delta_rule_prep")
+
+    def delta_rule_scan(self, proj: Act, cols, aux, cu_q, kv_len, slots, state, norm_w, norm_eps, out, heads, d,
+                        err) -> None:
+        """The recurrence over every entry's tokens, from and to ``state`` [slots, heads, d, d] (float;
+        an entry whose tokens open its request starts from zero), with the head norm and the gate:
+        ``out`` [n, heads d] in the model dtype."""
+        whole, parts, n_parts, stride = _split(proj)
+        self._check(self.lib.crane_delta_rule_scan(
+            _dt(out.dtype), whole, parts, n_parts, stride, int(cols), aux.data_ptr(), cu_q.data_ptr(),
+            kv_len.data_ptr(), slots.data_ptr(), state.shape[0], state.data_ptr(), norm_w.data_ptr(),
+            float(norm_eps), out.data_ptr(), kv_len.shape[0], heads, d, err.data_ptr(), self._stream(out)),
+            "delta_rule_scan")
+
     # ---- matrix product on the FP32 cores ------------------------------
     def gemm_simt(self, a, w, bias, out) -> None:
         """out[M,N] = a[M,K] @ w[N,K]^T (+ bias); rows may be strided."""
@@ -454,17 +557,19 @@ class Kernels:
 
     # ---- attention ------------------------------------------------------
     def paged_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table,
-                             page_size, nq, nkv, d, window, scale, err, dv=None, v_stride=None) -> None:
+                             page_size, nq, nkv, d, window, scale, err, dv=None, v_stride=None,
+                             sink: bool = False) -> None:
         """``dv``: width of a value row (default: the keys'), ``v_stride``: elements
         between value rows (default ``dv``).  With ``v_pool`` the key pool itself and
-        ``v_stride == d`` the values are the leading ``dv`` columns of the key rows."""
+        ``v_stride == d`` the values are the leading ``dv`` columns of the key rows.
+        ``sink``: the softmax has one more candidate of score 0 that has no value."""
         dv = d if dv is None else int(dv)
         v_stride = dv if v_stride is None else int(v_stride)
         self._check(self.lib.crane_paged_attention_simt(
             _dt(q.dtype), q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
             positions.data_ptr(), tok_entry.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, dv, v_stride,
-            int(window), float(scale), err.data_ptr(), self._stream(q)), "paged_attention_simt")
+            int(window), float(scale), 1 if sink else 0, err.data_ptr(), self._stream(q)), "paged_attention_simt")
 
     @staticmethod
     def decode_splits(entries: int, nkv: int, sms: int, cap: int = 64, max_keys: int = 1 << 30) -> int:

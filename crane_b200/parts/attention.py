@@ -188,3 +188,132 @@ class GqaAttention(Part):
                                    self.scale, rt.err)
             rt.launches += 2
         return rt.linear(o, self.o_w, self.o_b, "attn_out")
+
+
+@register_part("mixer", "sink_attention")
+class SinkAttention(Part):
+    """Grouped-query attention without positions, whose queries and keys are RMS-normed over
+    their whole projections (all heads at once, plain weights), whose values may be wider or
+    narrower than its keys, and whose softmax may have a sink: one more candidate of score 0
+    that has no value, p_j = exp(s_j) / (1 + sum_i exp(s_i)).
+    params: ``hidden_size``, ``heads``, ``kv_heads``, ``dim`` (query/key head), ``vdim`` (value
+    head), ``scale``, ``sink`` (default True), ``qk_norm`` (default True) + ``norm_eps``,
+    ``window`` (0: every earlier position), ``names`` (tensor names behind the prefix for q, k,
+    v, o, q_norm, k_norm).  Tensors: q [H dim, hidden], k [G dim, hidden], v [G vdim, hidden],
+    o [hidden, H vdim], q_norm [H dim], k_norm [G dim] (float)."""
+    kind = "mixer"
+    NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm"}
+
+    @classmethod
+    def _sizes(cls, a):
+        return (int(a["hidden_size"]), int(a["heads"]), int(a["kv_heads"]), int(a["dim"]), int(a["vdim"]))
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        w, H, G, d, m = cls._sizes(a)
+        nm = dict(cls.NAMES, **(a.get("names") or {}))
+        out = {p + nm["q"]: TensorSpec((H * d, w)), p + nm["k"]: TensorSpec((G * d, w)),
+               p + nm["v"]: TensorSpec((G * m, w)), p + nm["o"]: TensorSpec((w, H * m))}
+        if a.get("qk_norm", True):
+            out[p + nm["q_norm"]] = TensorSpec((H * d,), "float32", "scale")
+            out[p + nm["k_norm"]] = TensorSpec((G * d,), "float32", "scale")
+        return out
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        self.w, self.H, self.G, self.d, self.m = self._sizes(a)
+        nm = dict(self.NAMES, **(a.get("names") or {}))
+        if self.H % self.G:
+            raise ValueError(f"{p}: {self.H} query heads are not a multiple of {self.G} key/value heads")
+        if self.d > 1024 or self.m > 512:
+            raise ValueError(f"{p}: heads of {self.d} / {self.m} elements are wider than the attention kernels "
+                             "take (1024 / 512)")
+        self.scale = float(a["scale"])
+        self.sink = bool(a.get("sink", True))
+        self.window = int(a.get("window") or 0)
+        self.eps = float(a.get("norm_eps") or 0.0)
+        self.qkv_w = torch.cat([weights.pop(p + nm[n]) for n in ("q", "k", "v")], dim=0).contiguous()
+        self.cols = self.qkv_w.shape[0]
+        self.o_w = weights[p + nm["o"]]
+        norm = bool(a.get("qk_norm", True))
+        self.q_norm = weights[p + nm["q_norm"]] if norm else None
+        self.k_norm = weights[p + nm["k_norm"]] if norm else None
+        # On the bfloat16 path keys and values are stored at one common head size that the warp-level
+        # attention kernels are compiled for (zero-filled columns add nothing to a score, and the
+        # value columns beyond vdim are never read back); the 32-bit path stores them as wide as they are.
+        self.store = int(a.get("head_dim") or 0) if not rt.exact else 0
+        if self.store and not (rt.kernels.prefill_attention_supports(self.store, self.H, self.G)
+                               and rt.kernels.decode_attention_supports(self.store, self.H, self.G)):
+            self.store = 0
+        if self.sink and not getattr(rt.kernels, "mma_attention_takes_sink", False):
+            self.store = 0
+        self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "64"))
+
+    @staticmethod
+    def common_head_size(dim: int, vdim: int, sizes) -> int:
+        """The smallest head size of ``sizes`` that holds both a key and a value row (0: none)."""
+        fit = [s for s in sorted(sizes) if s >= max(dim, vdim)]
+        return fit[0] if fit else 0
+
+    def cache_need(self) -> CacheNeed:
+        if self.store:
+            return CacheNeed("kv", kv_heads=self.G, head_dim=self.store, window=self.window)
+        return CacheNeed("kv", kv_heads=self.G, head_dim=self.d, window=self.window, v_head_dim=self.m)
+
+    def forward(self, h, ctx, cache, rt):
+        n = h.shape[0]
+        k = rt.kernels
+        H, G, d, m = self.H, self.G, self.d, self.m
+        qkv = rt.linear(h, self.qkv_w, None, "attn_qkv")
+        table = ctx.block_tables[cache.group]
+        D = self.store or d
+        q = rt.ws.get("attn_q", n, H * D, rt.dtype)
+        k.projection_norm_cache(qkv, self.cols, ctx.positions, ctx.tok_entry, table, cache.page_size, self.q_norm,
+                                self.k_norm, self.eps, q, cache.k, cache.v, H, G, d, m, rt.err)
+        rt.launches += 1
+        if not self.store:
+            o = rt.ws.get("attn_o", n, H * m, rt.dtype)
+            k.paged_attention_simt(q, o, cache.k, cache.v, ctx.positions, ctx.tok_entry, table, cache.page_size,
+                                   H, G, d, self.window, self.scale, rt.err, dv=m, v_stride=m, sink=self.sink)
+            rt.launches += 1
+            return rt.linear(o, self.o_w, None, "attn_out")
+        # the warp-level kernels at the common head size; the output projection reads the leading
+        # vdim columns of every head
+        o = rt.ws.get("attn_o", n, H * D, rt.dtype)
+        rt.launches += sink_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, self.window, self.scale,
+                                              self.sink, self.max_splits)
+        if D != m:
+            packed = rt.ws.get("attn_o_packed", n, H * m, rt.dtype)
+            packed.view(n, H, m).copy_(o.view(n, H, D)[:, :, :m])
+            o = packed
+        return rt.linear(o, self.o_w, None, "attn_out")
+
+
+def sink_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, window, scale, sink, max_splits) -> int:
+    """Attention of q [n, H, D] over pools of head size D with the warp-level kernels: entries of
+    one token through the split-KV decode kernel where that pays, the others through the prefill
+    kernel.  Returns the launches."""
+    n = q.shape[0]
+    decode = ctx.max_q_len == 1 and n == ctx.n_entries
+    singles = 0 if decode else getattr(ctx, "single_entries", 0)
+    launches = 0
+    if decode or singles:
+        if decode:
+            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * G)))
+        else:
+            splits = min(8, k.decode_splits(singles, G, rt.num_sms, max_splits))
+        part_o = part_ml = None
+        if splits > 1:
+            rows = rt.max_decode_rows * H * 32
+            part_o = rt.ws.get("attn_part_o", rows, D, torch.float32, cap=rows)
+            part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
+        k.paged_decode_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table, cache.page_size, H, G, D,
+                                 window, scale, splits, part_o, part_ml, rt.err, sink=sink)
+        launches += 2 if splits > 1 else 1
+        if decode:
+            return launches
+    tiles = query_tiles(ctx, 64, skip_single=bool(singles))
+    k.paged_prefill_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table, cache.page_size, tiles, H, G, D,
+                              window, scale, rt.err, skip_single=bool(singles), sink=sink)
+    return launches + 1

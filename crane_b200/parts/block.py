@@ -5,6 +5,10 @@
 fused into the norm that follows it, so a block hands its last output on
 unadded ("pending") and receives the one of the block before it.
 
+``sandwich_residual``: every sublayer's result is normed before it is added,
+x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x))); then an optional per-layer
+token input joins the stream.
+
 ``parallel_depth_average``: both branches read norms of the same x, their sum
 is added once, and what the next layer reads is a weighted sum of all layer
 results so far.
@@ -15,7 +19,7 @@ import torch
 
 from ..weights.loader import TensorSpec
 from .base import Part, build_part, register_block, register_part
-from .norm import BranchSum, combine_and_norm
+from .norm import BranchSum, add_normed, combine_and_norm
 
 
 @register_block("prenorm_residual")
@@ -88,3 +92,96 @@ class ParallelDepthAverageBlock:
         a = self.mixer.forward(h1, ctx, cache, rt)
         f = self.ffn.forward(h2, ctx, rt) if self.ffn is not None else None
         return BranchSum(a, f, self.combine)
+
+
+@register_part("entry", "pass_entry")
+class PassEntry(Part):
+    """What joins the stream where a pass over repeated layers begins: row ``row`` of a
+    [times, size] tensor and, ``add_embedding``, the embedding output that the embedding part
+    kept (workspace buffer "embedding_output").  params: ``size``, ``times``, ``tensor`` (name).
+    The tensor is kept float: it is added to the float stream."""
+    kind = "entry"
+
+    @classmethod
+    def manifest(cls, spec):
+        a = spec.params
+        return {spec.prefix + a["tensor"]: TensorSpec((a["times"], a["size"]), "float32", "offset")}
+
+    def load(self, weights, rt):
+        self.rows = weights[self.prefix + self.params["tensor"]]
+        self.size = int(self.params["size"])
+
+    def forward(self, x, pending, ctx, rt, row: int, add_embedding: bool = False):
+        if pending is not None:
+            raise ValueError("a pass begins behind a block that has not added its last result to the stream")
+        kept = rt.ws.get("embedding_output", x.shape[0], self.size, torch.float32) if add_embedding else None
+        rt.kernels.stream_enter(x, kept, self.rows[row])
+        rt.launches += 1
+        return None
+
+
+@register_part("side", "token_side_input")
+class TokenSideInput(Part):
+    """A per-layer input from the token itself: e = table[token, offset : offset + dim];
+    g = gelu_tanh(W_gate x) * e; y = W_proj g; x += y / rms(y) * w (a plain weight).
+    params: ``hidden_size``, ``dim``, ``offset``, ``table_cols``, ``vocab_size``, ``eps``, ``table``
+    (the table's full tensor name: all layers share it), tensors behind the prefix: ``gate``
+    [dim, hidden], ``proj`` [hidden, dim], ``norm`` [hidden] (float)."""
+    kind = "side"
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        return {a["table"]: TensorSpec((a["vocab_size"], a["table_cols"])),
+                p + "gate": TensorSpec((a["dim"], a["hidden_size"])),
+                p + "proj": TensorSpec((a["hidden_size"], a["dim"])),
+                p + "norm": TensorSpec((a["hidden_size"],), "float32", "scale")}
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        self.table = weights[a["table"]]
+        self.gate, self.proj, self.weight = weights[p + "gate"], weights[p + "proj"], weights[p + "norm"]
+        self.dim, self.offset, self.eps, self.size = int(a["dim"]), int(a["offset"]), float(a["eps"]), int(a["hidden_size"])
+
+    def forward(self, x, x_model, ctx, rt):
+        """``x_model``: the stream in the model dtype (what the gate's product reads)."""
+        z = rt.linear(x_model, self.gate, None, "side_gate")
+        g = rt.ws.get("side_gated", x.shape[0], self.dim, rt.dtype)
+        rt.kernels.token_gate(z, ctx.tokens, self.table, self.offset, g, rt.err, getattr(ctx, "deferred_tokens", None))
+        rt.launches += 1
+        y = rt.linear(g, self.proj, None, "side_out")
+        add_normed(x, y, self, rt)
+
+
+@register_block("sandwich_residual")
+class SandwichResidualBlock:
+    """parts: ``norm1``, ``mixer``, ``norm1b``; unless the layer has no feed-forward ``norm2``,
+    ``ffn``, ``norm2b``; optionally ``side`` (a ``token_side_input``).  Each addition of a normed
+    result is one kernel with the norm that reads the stream next.  The block leaves nothing
+    pending: its last addition needs the result's own norm first."""
+
+    def __init__(self, layer_spec):
+        p = layer_spec.parts
+        self.norm1, self.mixer, self.norm1b = (build_part(p[k]) for k in ("norm1", "mixer", "norm1b"))
+        self.ffn = build_part(p["ffn"]) if "ffn" in p else None
+        self.norm2 = build_part(p["norm2"]) if self.ffn is not None else None
+        self.norm2b = build_part(p["norm2b"]) if self.ffn is not None else None
+        self.side = build_part(p["side"]) if "side" in p else None
+
+    def parts(self):
+        return [q for q in (self.norm1, self.mixer, self.norm1b, self.norm2, self.ffn, self.norm2b, self.side)
+                if q is not None]
+
+    def forward(self, x, pending, ctx, cache, rt):
+        h = self.norm1.forward(x, pending, rt)
+        a = self.mixer.forward(h, ctx, cache, rt)
+        raw_name = "stream_model" if self.side is not None else None
+        if self.ffn is None:
+            _, raw = add_normed(x, a, self.norm1b, rt, raw_name=raw_name)
+        else:
+            h2, _ = add_normed(x, a, self.norm1b, rt, then=self.norm2, name="normed2")
+            f = self.ffn.forward(h2, ctx, rt)
+            _, raw = add_normed(x, f, self.norm2b, rt, raw_name=raw_name)
+        if self.side is not None:
+            self.side.forward(x, raw, ctx, rt)
+        return None

@@ -103,3 +103,35 @@ class BigramEmbedding(Part):
                                     self.mul_cur, ctx.positions, ctx.tok_entry, ctx.cu_q, ctx.slots, state,
                                     rt.err, deferred)
         rt.launches += 1
+
+
+@register_part("embed", "sinusoid_embedding")
+class SinusoidEmbedding(Part):
+    """x0 = E[token] + s(position): column 2i of s is sin(p f_i), column 2i + 1 is cos(p f_i),
+    f_i = base^(-2i / hidden).  params: ``vocab_size``, ``hidden_size``, ``table`` (tensor name),
+    ``base`` (default 10000), ``keep_copy`` (the rows are also written to the workspace buffer
+    "embedding_output", for a model that adds the embedding output again later).  Tensor E [V,H].
+    The f_i are formed in 64-bit on the host and the angle p f_i in 64-bit on the device."""
+    kind = "embed"
+    needs_context = True          # it reads the tokens' positions
+    KEPT = "embedding_output"
+
+    @classmethod
+    def manifest(cls, spec):
+        a = spec.params
+        return {spec.prefix + a.get("table", "weight"): TensorSpec((a["vocab_size"], a["hidden_size"]))}
+
+    def load(self, weights, rt):
+        a = self.params
+        self.table = weights[self.prefix + a.get("table", "weight")]
+        self.hidden = int(a["hidden_size"])
+        base = float(a.get("base") or 10000.0)
+        half = (self.hidden + 1) // 2
+        self.freq = torch.tensor([base ** (-2.0 * i / self.hidden) for i in range(half)], dtype=torch.float64,
+                                 device=rt.device)
+        self.keep_copy = bool(a.get("keep_copy"))
+
+    def forward(self, tokens, x, rt, deferred=None, ctx=None, cache=None):
+        keep = rt.ws.get(self.KEPT, x.shape[0], self.hidden, torch.float32) if self.keep_copy else None
+        rt.kernels.embed_sinusoid(tokens, ctx.positions, self.table, self.freq, x, keep, rt.err, deferred)
+        rt.launches += 1

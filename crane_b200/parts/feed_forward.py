@@ -77,3 +77,99 @@ class XieluMlp(Part):
         rt.kernels.xielu(up, act, self.pq)
         rt.launches += 1
         return rt.linear(act, self.down, None, "ffn_down")
+
+
+@register_part("ffn", "act_mlp")
+class ActMlp(Part):
+    """down(act(up(h))), no biases.  params: ``hidden_size``, ``intermediate_size``, ``act``
+    ("relu2": the square of relu, "gelu": the erf form, "gelu_tanh"), ``names`` (up, down).
+    Tensors: up [I,H], down [H,I]."""
+    kind = "ffn"
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        nm = dict({"up": "up", "down": "down"}, **(a.get("names") or {}))
+        h, i = a["hidden_size"], a["intermediate_size"]
+        return {p + nm["up"]: TensorSpec((i, h)), p + nm["down"]: TensorSpec((h, i))}
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        nm = dict({"up": "up", "down": "down"}, **(a.get("names") or {}))
+        self.inter, self.act = int(a["intermediate_size"]), str(a["act"])
+        if self.act not in rt.kernels.ACTIVATIONS:
+            raise ValueError(f"{p}: no activation '{self.act}'; there are: {', '.join(rt.kernels.ACTIVATIONS)}")
+        self.up, self.down = weights[p + nm["up"]], weights[p + nm["down"]]
+
+    def forward(self, h, ctx, rt):
+        up = rt.linear(h, self.up, None, "ffn_up")
+        act = rt.ws.get("ffn_act", h.shape[0], self.inter, rt.dtype)
+        rt.kernels.ffn_activation(up, act, self.act)
+        rt.launches += 1
+        return rt.linear(act, self.down, None, "ffn_down")
+
+
+@register_part("ffn", "routed_experts")
+class RoutedExperts(Part):
+    """A mixture of small feed-forwards down_e(act(up_e(h))): the router's logits z = W_r h are
+    formed in 32-bit, the ``top`` largest choose a token's experts (ties to the lower index), and
+    their weights are the softmax over the chosen logits alone.  An optional shared expert of the
+    same form runs for every token and is added.
+    params: ``hidden_size``, ``experts``, ``top``, ``expert_size``, ``shared_size`` (0: none), ``act``,
+    ``names`` (router, expert: a pattern with {e}, shared, up, down).
+    Tensors: router [E,H]; per expert up [F,H], down [H,F]; shared up [Fs,H], down [H,Fs].
+
+    All experts' up matrices (and the shared one's) are one matrix, and so are the down matrices:
+    a step is two products with the activation between them, which multiplies every expert's
+    columns by the token's routing weight (zero for experts that it did not choose).  The result
+    of a token does not depend on what else is in the batch."""
+    kind = "ffn"
+    NAMES = {"router": "router", "expert": "e{e}.", "shared": "shared.", "up": "up", "down": "down"}
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        nm = dict(cls.NAMES, **(a.get("names") or {}))
+        h, E, F, Fs = int(a["hidden_size"]), int(a["experts"]), int(a["expert_size"]), int(a.get("shared_size") or 0)
+        m = {p + nm["router"]: TensorSpec((E, h))}
+        for e in range(E):
+            q = p + nm["expert"].format(e=e)
+            m[q + nm["up"]] = TensorSpec((F, h))
+            m[q + nm["down"]] = TensorSpec((h, F))
+        if Fs:
+            m[p + nm["shared"] + nm["up"]] = TensorSpec((Fs, h))
+            m[p + nm["shared"] + nm["down"]] = TensorSpec((h, Fs))
+        return m
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        nm = dict(self.NAMES, **(a.get("names") or {}))
+        self.E, self.top, self.F = int(a["experts"]), int(a["top"]), int(a["expert_size"])
+        self.Fs, self.act = int(a.get("shared_size") or 0), str(a["act"])
+        if not 0 < self.top <= self.E:
+            raise ValueError(f"{p}: {self.top} of {self.E} experts cannot be chosen")
+        if self.act not in rt.kernels.ACTIVATIONS:
+            raise ValueError(f"{p}: no activation '{self.act}'; there are: {', '.join(rt.kernels.ACTIVATIONS)}")
+        self.router = weights[p + nm["router"]]
+        ups = [weights.pop(p + nm["expert"].format(e=e) + nm["up"]) for e in range(self.E)]
+        downs = [weights.pop(p + nm["expert"].format(e=e) + nm["down"]) for e in range(self.E)]
+        if self.Fs:
+            ups.append(weights.pop(p + nm["shared"] + nm["up"]))
+            downs.append(weights.pop(p + nm["shared"] + nm["down"]))
+        self.up = torch.cat(ups, dim=0).contiguous()                 # [E F + Fs, H]
+        self.down = torch.cat(downs, dim=1).contiguous()             # [H, E F + Fs]
+        self.inter = self.up.shape[0]
+
+    def forward(self, h, ctx, rt):
+        n = h.shape[0]
+        k = rt.kernels
+        logits = rt.linear(h, self.router, None, "router_logits", out_dtype=torch.float32)
+        route = rt.ws.get("route_weights", n, self.E, torch.float32)
+        idx = rt.ws.get("route_idx", n, self.top, torch.int32)
+        wt = rt.ws.get("route_wt", n, self.top, torch.float32)
+        k.route_topk(logits, route, idx, wt)
+        up = rt.linear(h, self.up, None, "experts_up")
+        act = rt.ws.get("experts_act", n, self.inter, rt.dtype)
+        k.ffn_activation(up, act, self.act, route, self.F, self.E * self.F)
+        rt.launches += 2
+        return rt.linear(act, self.down, None, "experts_down")

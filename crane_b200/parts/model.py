@@ -23,7 +23,7 @@ def _block_part_specs(layer_spec):
 def model_manifest(spec: ModelSpec) -> Dict[str, TensorSpec]:
     """Every tensor the model expects, from the manifests of its parts."""
     out: Dict[str, TensorSpec] = {}
-    specs = [spec.embed, spec.final_norm, spec.head]
+    specs = [spec.embed, spec.final_norm, spec.head] + ([spec.entry] if spec.entry is not None else [])
     for layer in spec.layers:
         specs.extend(_block_part_specs(layer))
     for ps in specs:
@@ -43,15 +43,20 @@ class DecoderModel:
         self.embed = build_part(spec.embed)
         self.final_norm = build_part(spec.final_norm)
         self.head = build_part(spec.head)
+        self.entry = build_part(spec.entry) if spec.entry is not None else None
         self.blocks = [block_class(l.block)(l) for l in spec.layers]
         # the head may share the embedding's tensor, so it loads before any part pops tensors
         self.embed.load(weights, rt)
         self.head.load(weights, rt)
         self.final_norm.load(weights, rt)
+        if self.entry is not None:
+            self.entry.load(weights, rt)
         for b in self.blocks:
             for part in b.parts():
                 part.load(weights, rt)
         for place, step in enumerate(spec.schedule):
+            if step.enter is not None and self.entry is None:
+                raise ValueError(f"schedule step {place} has an entry, the model has no entry part")
             if not 0 <= step.layer < len(self.blocks):
                 raise ValueError(f"schedule step {place} names layer {step.layer}, which does not exist")
             src = step.cache_step(place)
@@ -72,7 +77,7 @@ class DecoderModel:
 
     def capturable(self) -> bool:
         """Whether every part says that its forward can be recorded in a CUDA graph."""
-        parts = [self.embed, self.final_norm, self.head]
+        parts = [self.embed, self.final_norm, self.head] + ([self.entry] if self.entry is not None else [])
         for b in self.blocks:
             parts += list(b.parts())
         return all(getattr(p, "capturable", True) for p in parts)
@@ -101,12 +106,14 @@ class DecoderModel:
         n = ctx.n_tokens
         x = rt.ws.get("residual", n, self.spec.hidden_size, torch.float32)
         if getattr(self.embed, "needs_context", False):
-            self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None), ctx=ctx,
-                               cache=caches[len(self.spec.schedule)])
+            own = caches[len(self.spec.schedule)] if hasattr(self.embed, "cache_need") else None
+            self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None), ctx=ctx, cache=own)
         else:
             self.embed.forward(ctx.tokens, x, rt, getattr(ctx, "deferred_tokens", None))
         pending = None
         for place, step in enumerate(self.spec.schedule):
+            if step.enter is not None:
+                pending = self.entry.forward(x, pending, ctx, rt, **step.enter)
             pending = self.blocks[step.layer].forward(x, pending, ctx, caches[step.cache_step(place)], rt)
         if ctx.n_want == 0:
             if pending is not None:

@@ -12,15 +12,23 @@ from .base import Part, register_part
 
 @register_part("norm", "rms_norm")
 class RMSNorm(Part):
-    """params: ``size``, ``eps``.  Tensor: ``<prefix>weight`` [size], kept float."""
+    """params: ``size``, ``eps``; ``weight`` (tensor name behind the prefix, default "weight");
+    ``weight_offset`` (the norm multiplies by offset + w: 0, or 1 for weights stored around
+    zero; folded into the weight when it is loaded).  Tensor [size], kept float."""
     kind = "norm"
 
     @classmethod
     def manifest(cls, spec):
-        return {spec.prefix + "weight": TensorSpec((spec.params["size"],), "float32")}
+        offset = float(spec.params.get("weight_offset") or 0.0)
+        return {spec.prefix + spec.params.get("weight", "weight"):
+                TensorSpec((spec.params["size"],), "float32", "offset" if offset else "scale" if
+                           "weight" in spec.params else "")}
 
     def load(self, weights, rt):
-        self.weight = weights[self.prefix + "weight"]
+        self.weight = weights[self.prefix + self.params.get("weight", "weight")]
+        offset = float(self.params.get("weight_offset") or 0.0)
+        if offset:
+            self.weight = (self.weight + offset).contiguous()
         self.eps = float(self.params["eps"])
         self.size = int(self.params["size"])
 
@@ -33,6 +41,19 @@ class RMSNorm(Part):
         rt.kernels.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
         rt.launches += 1
         return out
+
+
+def add_normed(x, delta, norm, rt, then=None, name="normed", raw_name=None):
+    """x += norm(delta) (an ``rms_norm`` part applied to a sublayer's result before it joins the
+    float stream) and, in the same kernel, ``then`` (another ``rms_norm`` part) of the new stream
+    and/or the stream itself in the model dtype (``raw_name``).  Returns (normed, raw)."""
+    n = x.shape[0]
+    out = rt.ws.get(name, n, norm.size, rt.dtype) if then is not None else None
+    raw = rt.ws.get(raw_name, n, norm.size, rt.dtype) if raw_name is not None else None
+    rt.kernels.add_normed_norm(x, delta, norm.weight, norm.eps, then.weight if then is not None else None,
+                               then.eps if then is not None else 0.0, out, raw)
+    rt.launches += 1
+    return out, raw
 
 
 class BranchSum:

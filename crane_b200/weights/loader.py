@@ -49,6 +49,9 @@ class TensorSpec:
     # "scale" (1 + noise: a norm's weight), "offset" (noise: a bias), "mix" (weights of an average
     # over the tensor's length), "unit" (numbers of order one)
     init: str = ""
+    # a dimension of -1 in ``shape`` is read from the stored tensor (a size that the configuration does
+    # not state); ``free`` is what random weights take for it
+    free: int = 0
 
 
 def _target_dtype(spec: TensorSpec, stored: torch.dtype, model_dtype: torch.dtype) -> torch.dtype:
@@ -71,7 +74,7 @@ def load_weights(source, manifest: Mapping[str, TensorSpec], ignored: Mapping[st
     for n, spec in manifest.items():
         if n in have:
             _, shape = source.info(n)
-            if tuple(shape) != tuple(spec.shape):
+            if len(shape) != len(spec.shape) or any(e not in (-1, f) for e, f in zip(spec.shape, shape)):
                 wrong.append((n, tuple(spec.shape), tuple(shape)))
     if missing or unexpected or wrong:
         raise WeightsError(missing, unexpected, sorted(wrong), where)

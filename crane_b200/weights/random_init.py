@@ -36,13 +36,16 @@ def random_tensors(manifest: Dict[str, TensorSpec], seed: int, dtype: torch.dtyp
         spec = manifest[name]
         gen = torch.Generator(device=dev)
         gen.manual_seed(_tensor_seed(seed, name))
-        t = torch.randn(spec.shape, generator=gen, device=dev, dtype=torch.float32)
+        shape = tuple(spec.free if n == -1 else n for n in spec.shape)
+        t = torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)
         is_norm_like = spec.init == "scale" or (not spec.init and spec.keep == "float32"
                                                 and name.endswith("weight"))
         if is_norm_like:
             out[name] = (1.0 + norm_std * t)
         elif spec.init == "mix":
             out[name] = (1.0 + 0.5 * t) / t.numel()
+        elif spec.init == "offset":
+            out[name] = std * t
         elif spec.init == "unit":
             out[name] = 0.5 * t
         elif spec.keep == "float32":
