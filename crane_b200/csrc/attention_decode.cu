@@ -54,6 +54,8 @@ struct FusedArgs {
     __nv_bfloat16* v_pool_w;
     RopeParams rope;                // pairing, rotated width, norm order, norm weight offset
     int general;                    // 0: the defaults (whole head, contiguous halves, norm after, plain w)
+    int sink;                       // (the plain form too) the softmax has one more candidate of score 0 that
+                                    // has no value: exp2(0 - max) joins the sum where the output is divided
 };
 
 // A single element of the raw product (see raw2 for pairs).
@@ -495,6 +497,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
         }
         const int h = g * n_rep + r;
         if (n_splits == 1) {
+            if (fa.sink) L += exp2f(-mb);
             out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
         } else {
             const long long pi = ((long long)e * nq + h) * n_splits + split;
@@ -958,6 +961,7 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
         }
         const int h = g * n_rep + r;
         if (n_splits == 1) {
+            if (fa.sink) L += exp2f(-mb);
             out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
         } else if (CLUSTER) {
             cl_o[r * D + c] = O;
@@ -1003,6 +1007,7 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
                 L += f * ml[sp].y;
                 acc += f * ov[sp];
             }
+            if (fa.sink) L += exp2f(-mb);
             out[((long long)t * nq + g * n_rep + r) * D + (idx % D)] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         }
         // nobody leaves while a CTA of the cluster may still read its shared memory
@@ -1016,7 +1021,7 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
 template <int MAXS>
 __device__ __forceinline__ void merge_column(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                              __nv_bfloat16* __restrict__ out, long long base, int t, int nq,
-                                             int h, int d, int n_splits) {
+                                             int h, int d, int n_splits, int sink) {
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float2 ml[MAXS];
         float o[MAXS];
@@ -1036,6 +1041,7 @@ __device__ __forceinline__ void merge_column(const float* __restrict__ part_o, c
             L += f * ml[s].y;
             acc += f * o[s];
         }
+        if (sink) L += exp2f(-mb);
         out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
 }
@@ -1048,7 +1054,7 @@ __device__ __forceinline__ void merge_column(const float* __restrict__ part_o, c
 // four loads in flight per thread.  Always in slice order.
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
-                                    int nq, int d, int n_splits) {
+                                    int nq, int d, int n_splits, int sink) {
     __shared__ float wgt[64];
     __shared__ float m_s[64], l_s[64];
     pdl_launch_dependents();
@@ -1059,9 +1065,9 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     if (cu_q[e + 1] - t != 1) return;
     if (n_splits <= 64) {
         // all loads of a thread go out together; 16 slices' worth of registers when that is enough
-        if (n_splits <= 16) merge_column<16>(part_o, part_ml, out, base, t, nq, h, d, n_splits);
-        else if (n_splits <= 32) merge_column<32>(part_o, part_ml, out, base, t, nq, h, d, n_splits);
-        else merge_column<64>(part_o, part_ml, out, base, t, nq, h, d, n_splits);
+        if (n_splits <= 16) merge_column<16>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink);
+        else if (n_splits <= 32) merge_column<32>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink);
+        else merge_column<64>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink);
         return;
     }
     for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
@@ -1079,6 +1085,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
             L += f * l_s[s];
             wgt[s] = f;
         }
+        if (sink) L += exp2f(-mb);
         const float inv = L > 0.f ? 1.f / L : 0.f;
         for (int s = 0; s < n_splits; ++s) wgt[s] *= inv;
     }
@@ -1219,7 +1226,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
         if (n_splits > 1 && !cluster)
             return crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
                                 (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq,
-                                D, n_splits);
+                                D, n_splits, fa.sink);
         return 0;
     }
     int rc = crane_launch(kern, grid, dim3(WARPS * 32), smem, st, (const __nv_bfloat16*)q,
@@ -1229,7 +1236,7 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
     if (rc == 0 && n_splits > 1)
         rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
                           (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq, D,
-                          n_splits);
+                          n_splits, fa.sink);
     return rc;
 }
 }  // namespace
@@ -1298,12 +1305,13 @@ CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part
                                            const void* k_pool, const void* v_pool, const int* cu_q,
                                            const int* kv_len, const int* block_table, int max_blocks,
                                            int num_pages, int page_size, int n_entries, int nq, int nkv,
-                                           int d, int window, float scale, int n_splits, int* err,
-                                           cudaStream_t st) {
+                                           int d, int window, float scale, int n_splits, int sink,
+                                           int* err, cudaStream_t st) {
     if (n_entries <= 0) return 0;
     if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64)
         return (int)cudaErrorInvalidValue;
-    const FusedArgs none = {};
+    FusedArgs none = {};
+    none.sink = sink;
     return launch_for_head_size(d, 0, q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, block_table,
                                 max_blocks, num_pages, page_size, n_entries, nq, nkv, window, scale,
                                 n_splits, err, &none, st);
@@ -1407,6 +1415,6 @@ CRANE_API int crane_paged_decode_attention_noalloc(const void* q, void* out, con
     }
     return crane_paged_decode_attention(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
                                         block_table, max_blocks, num_pages, page_size, n_entries, nq,
-                                        nkv, d, window, scale, n_splits, err, stream);
+                                        nkv, d, window, scale, n_splits, 0, err, stream);
 }
 #endif  // CRANE_HEAD_SIZE

@@ -28,7 +28,7 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
                           const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_q,
                           const int* __restrict__ kv_len, const int* __restrict__ block_table,
                           int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
-                          int window, float scale_log2, int skip_single, int* err) {
+                          int window, float scale_log2, int skip_single, int sink, int* err) {
     constexpr int RB = Tile<D>::ROW_BYTES;
     constexpr int TILE_BYTES = BKV * RB;
     constexpr int KS = D / 16, DN = D / 8;
@@ -186,6 +186,10 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
     if (__any_sync(0xffffffffu, bad_page) && lane == 0) atomicOr(err, CRANE_ERR_PAGE_RANGE);
     l[0] = quad_sum(l[0]);
     l[1] = quad_sum(l[1]);
+    if (sink) {                                      // one more candidate of score 0 that has no value
+        l[0] += exp2f(-m[0]);
+        l[1] += exp2f(-m[1]);
+    }
     const float inv_a = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_b = l[1] > 0.f ? 1.f / l[1] : 0.f;
     const int c0 = (lane & 3) * 2;
 #pragma unroll
@@ -203,7 +207,7 @@ template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* cu_q,
                    const int* kv_len, const int* block_table, int max_blocks, int num_pages,
                    int page_size, int n_entries, int total_q_tiles, int nq, int nkv, int window,
-                   float scale, int skip_single, int* err, cudaStream_t st) {
+                   float scale, int skip_single, int sink, int* err, cudaStream_t st) {
     constexpr int smem = 4 * BKV * Tile<D>::ROW_BYTES;
     auto kern = paged_prefill_attn_kernel<D>;
     static bool configured = false;
@@ -216,7 +220,7 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
     kern<<<grid, THREADS, smem, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
                                       kv_len, block_table, max_blocks, num_pages, page_size, n_entries,
-                                      nq, nkv, window, scale * 1.4426950408889634f, skip_single, err);
+                                      nq, nkv, window, scale * 1.4426950408889634f, skip_single, sink, err);
     return crane_launch_status();
 }
 }  // namespace
@@ -228,13 +232,13 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
 #define CRANE_PREFILL_LAUNCHER_ARGS                                                                    \
     const void *q, void *out, const void *k_pool, const void *v_pool, const int *cu_q, const int *kv_len, \
         const int *block_table, int max_blocks, int num_pages, int page_size, int n_entries,            \
-        int total_q_tiles, int nq, int nkv, int window, float scale, int skip_single, int *err,         \
+        int total_q_tiles, int nq, int nkv, int window, float scale, int skip_single, int sink, int *err, \
         cudaStream_t st
 #ifdef CRANE_HEAD_SIZE
 extern "C" int CRANE_CAT(crane_prefill_launch_d, CRANE_HEAD_SIZE)(CRANE_PREFILL_LAUNCHER_ARGS) {
     return launch_prefill<CRANE_HEAD_SIZE>(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks,
                                            num_pages, page_size, n_entries, total_q_tiles, nq, nkv, window,
-                                           scale, skip_single, err, st);
+                                           scale, skip_single, sink, err, st);
 }
 #else
 #ifdef CRANE_HEAD_SIZE_LIST          // the head sizes linked into this library (see attention_decode.cu)
@@ -262,14 +266,14 @@ CRANE_API int crane_paged_prefill_attention(const void* q, void* out, const void
                                             const int* block_table, int max_blocks, int num_pages,
                                             int page_size, int n_entries, int total_q_tiles, int nq,
                                             int nkv, int d, int window, float scale, int skip_single,
-                                            int* err, cudaStream_t st) {
+                                            int sink, int* err, cudaStream_t st) {
     if (n_entries <= 0 || total_q_tiles <= 0) return 0;
     if (!crane_paged_prefill_attention_supports(d, nq, nkv)) return (int)cudaErrorInvalidValue;
 #define CASE(DD)                                                                                      \
     case DD:                                                                                          \
         return crane_prefill_launch_d##DD(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks, \
                                           num_pages, page_size, n_entries, total_q_tiles, nq, nkv,      \
-                                          window, scale, skip_single, err, st);
+                                          window, scale, skip_single, sink, err, st);
     switch (d) { CRANE_PREFILL_HEAD_SIZES(CASE) }
 #undef CASE
     return (int)cudaErrorInvalidValue;

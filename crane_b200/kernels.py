@@ -30,9 +30,9 @@ _SIGNATURES = {
     "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
-    "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
+    "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
     "crane_paged_prefill_attention_supports": [I, I, I],
-    "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+    "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P],
     "crane_paged_decode_attention_fused": [P, P, I, L, I, I, I, P, P, I, P, P, F, P, P, P, P, P, P, P, P,
                                            I, I, I, I, I, I, I, I, F, I, I, I, I, F, P, P],
     "crane_prefill_attention_tc_supports": [I, I, I, I],
@@ -317,6 +317,7 @@ class Kernels:
             deferred.numel() if deferred is not None else 0, err.data_ptr(), self._stream(out)), "token_gate")
 
     ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2}
+    mma_attention_takes_sink = True      # the warp-level attention kernels (prompt portions and decoded tokens) have the option
 
     def ffn_activation(self, up: Act, out, kind: str, route=None, per_expert: int = 0, routed_cols: int = 0) -> None:
         """out = act(up), times ``route[t, c // per_expert]`` (float [rows, experts]) for the leading
@@ -620,33 +621,36 @@ class Kernels:
         return bool(self.lib.crane_paged_decode_attention_supports(d, nq, nkv))
 
     def paged_decode_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
-                               nq, nkv, d, window, scale, n_splits, part_o, part_ml, err) -> None:
+                               nq, nkv, d, window, scale, n_splits, part_o, part_ml, err, sink: bool = False) -> None:
         """The entries of exactly one token (bfloat16); entries with more or no
         rows are skipped.  ``part_o`` [entries * nq * n_splits * d] and ``part_ml``
-        [entries * nq * n_splits * 2] floats are scratch for n_splits > 1."""
+        [entries * nq * n_splits * 2] floats are scratch for n_splits > 1.  ``sink``: the
+        softmax has one more candidate of score 0 that has no value."""
         n_entries = kv_len.shape[0]
         self.require_head_size(d)
         self._check(self.lib.crane_paged_decode_attention(
             q.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml), k_pool.data_ptr(),
             v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], k_pool.shape[0], page_size, n_entries, nq, nkv, d, int(window),
-            float(scale), int(n_splits), err.data_ptr(), self._stream(q)), "paged_decode_attention")
+            float(scale), int(n_splits), 1 if sink else 0, err.data_ptr(), self._stream(q)), "paged_decode_attention")
 
     def prefill_attention_supports(self, d: int, nq: int, nkv: int) -> bool:
         self.require_head_size(d)
         return bool(self.lib.crane_paged_prefill_attention_supports(d, nq, nkv))
 
     def paged_prefill_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
-                                total_q_tiles, nq, nkv, d, window, scale, err, skip_single=False) -> None:
+                                total_q_tiles, nq, nkv, d, window, scale, err, skip_single=False,
+                                sink: bool = False) -> None:
         """Any mix of portions and single tokens (bfloat16).  ``total_q_tiles``:
         the sum over the entries of ceil(tokens / 64), or more.  ``skip_single``:
-        entries of exactly one token are left to the decode kernel."""
+        entries of exactly one token are left to the decode kernel.  ``sink`` as in
+        ``paged_decode_attention``."""
         self.require_head_size(d)
         self._check(self.lib.crane_paged_prefill_attention(
             q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(),
             kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], k_pool.shape[0],
             page_size, kv_len.shape[0], int(total_q_tiles), nq, nkv, d, int(window), float(scale),
-            1 if skip_single else 0, err.data_ptr(), self._stream(q)), "paged_prefill_attention")
+            1 if skip_single else 0, 1 if sink else 0, err.data_ptr(), self._stream(q)), "paged_prefill_attention")
 
     def prefill_attention_tc_supports(self, d: int, nq: int, nkv: int, page_size: int) -> bool:
         return bool(self.lib.crane_prefill_attention_tc_supports(d, nq, nkv, page_size))

@@ -248,6 +248,10 @@ class SinkAttention(Part):
             self.store = 0
         if self.sink and not getattr(rt.kernels, "mma_attention_takes_sink", False):
             self.store = 0
+        if self.store and self.store != self.m:
+            wide = torch.zeros((self.w, self.H, self.store), dtype=self.o_w.dtype, device=self.o_w.device)
+            wide[:, :, :self.m] = self.o_w.view(self.w, self.H, self.m)
+            self.o_w = wide.view(self.w, self.H * self.store).contiguous()
         self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "64"))
 
     @staticmethod
@@ -278,15 +282,11 @@ class SinkAttention(Part):
                                    H, G, d, self.window, self.scale, rt.err, dv=m, v_stride=m, sink=self.sink)
             rt.launches += 1
             return rt.linear(o, self.o_w, None, "attn_out")
-        # the warp-level kernels at the common head size; the output projection reads the leading
-        # vdim columns of every head
+        # the warp-level kernels at the common head size; the output projection's matrix has zero
+        # columns where a stored head is wider than vdim
         o = rt.ws.get("attn_o", n, H * D, rt.dtype)
         rt.launches += sink_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, self.window, self.scale,
                                               self.sink, self.max_splits)
-        if D != m:
-            packed = rt.ws.get("attn_o_packed", n, H * m, rt.dtype)
-            packed.view(n, H, m).copy_(o.view(n, H, D)[:, :, :m])
-            o = packed
         return rt.linear(o, self.o_w, None, "attn_out")
 
 

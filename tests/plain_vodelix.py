@@ -223,3 +223,14 @@ def forward(cfg, w, tokens, keep_layers=False):
         kept.append(x.copy())
     logits = rms_norm(x, w["final.norm"], cfg["norm"]["eps"], 1.0) @ w["embed"].T
     return (logits, np.stack(kept)) if keep_layers else logits
+
+
+def logits_all(cfg, w, tokens):
+    return forward(cfg, w, tokens)
+
+
+def greedy_generate(cfg, w, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(np.argmax(forward(cfg, w, toks)[-1])))
+    return toks

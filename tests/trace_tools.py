@@ -182,12 +182,14 @@ def _base(name: str) -> str:
     return name.rstrip("tpm") if name[-1] in "tpm" else name
 
 
-def compare_cuts(runs: Sequence[Tuple[Dict[int, np.ndarray], "TraceBuilder"]], dtype: str, label: str = "") -> float:
+def compare_cuts(runs: Sequence[Tuple[Dict[int, np.ndarray], "TraceBuilder"]], dtype: str, label: str = "",
+                 tol: float = 0.0) -> float:
     """runs: (logits by step, the trace that asked for them) of one model.  Every
     (request, position) that was wanted more than once is compared with its
     first occurrence.  Returns the worst relative root-mean-square difference."""
     first: Dict[Tuple[str, int], Tuple[np.ndarray, str]] = {}
     worst, pairs = 0.0, 0
+    tol = tol or TOL_CUTS[dtype]
     for got, tb in runs:
         for sid in sorted(tb.rows):
             for i, (r, p) in enumerate(tb.rows[sid]):
@@ -199,9 +201,9 @@ def compare_cuts(runs: Sequence[Tuple[Dict[int, np.ndarray], "TraceBuilder"]], d
                 d = float(np.sqrt(((row - ref) ** 2).mean()) / np.sqrt((ref ** 2).mean()))
                 pairs += 1
                 worst = max(worst, d)
-                assert d <= TOL_CUTS[dtype], (
+                assert d <= tol, (
                     f"{label} {dtype}: request {key[0]} position {p} differs between {where} and step {sid} "
-                    f"as {r}: relative rms difference {d:.3e} > {TOL_CUTS[dtype]:.1e}")
+                    f"as {r}: relative rms difference {d:.3e} > {tol:.1e}")
     print(f"{label} {dtype}: {pairs} positions computed more than once, worst difference between cuttings {worst:.3e}")
     return worst
 
