@@ -1335,7 +1335,7 @@ CRANE_API int crane_paged_decode_attention_fused(
     if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64 || (d & 3) ||
         (qkv_stride & 1) || (part_stride & 1) || rotary_dim > d || (rotary_dim & 1))
         return (int)cudaErrorInvalidValue;
-    FusedArgs fa;
+    FusedArgs fa = {};
     fa.rope = RopeParams{rotary_dim, interleaved ? 1 : 0, norm_first ? 1 : 0, norm_offset};
     fa.general = rope_is_default(fa.rope, d) ? 0 : 1;
     fa.qkv = (const __nv_bfloat16*)qkv; fa.qkv_parts = qkv_parts; fa.n_parts = n_parts;
