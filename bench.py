@@ -605,6 +605,192 @@ def radorax_workload(args, pk):
     return out
 
 
+def vodelix_config(like, layers):
+    """A Vodelix model with the width, layer count and vocabulary of the Hunyuan configuration `like`:
+    of every four layers one attends (the other's head counts, heads of 128) and three run the delta
+    rule (heads of 64 across the width); every other layer has a dense feed-forward of the other's
+    inner size, the rest eight experts of a quarter of it, two chosen, and a shared one; layers 1 and
+    2 run twice; a token input of 64 per layer."""
+    h, heads, kv = like["hidden_size"], like["num_attention_heads"], like["num_key_value_heads"]
+    ff = like["intermediate_size"]
+    att = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    delta = {"heads": h // 64, "dim": 64, "decay_rank": 64}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    ls = [{"type": "attention" if i % 4 == 1 else "general_delta", "mixer": att if i % 4 == 1 else delta,
+           "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]
+    cfg = {"architecture": "Vodelix", "vocab": like["vocab_size"], "width": h, "norm": {"eps": 1e-5},
+           "token_side": {"dim": 64}, "layers": ls}
+    if layers >= 3:
+        cfg["loop"] = {"start": 1, "stop": 3, "times": 2}
+    return cfg
+
+
+def vodelix_kernel_table(vcfg, hcfg, pk, tokens, batch, context):
+    """Every kernel that only Vodelix runs beside the kernel of Hunyuan Dense that does the like job,
+    each alone on synthetic operands of the two models' layer sizes (L2 flushed between repetitions),
+    with the fraction of its roofline: algorithmic bytes over the measured copy rate, or FLOPs over
+    the measured bf16 rate, whichever takes longer."""
+    import math
+    import numpy as np
+    import torch
+    from crane_b200.kernels import get_kernels
+    K = get_kernels([hcfg["head_dim"]])
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    W = vcfg["width"]
+    dl = next(l["mixer"] for l in vcfg["layers"] if l["type"] == "general_delta")
+    H, dd, R = dl["heads"], dl["dim"], dl["decay_rank"]
+    ffh = hcfg["intermediate_size"]
+    d, nq, nkv = hcfg["head_dim"], hcfg["num_attention_heads"], hcfg["num_key_value_heads"]
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, like, ms, nbytes, flops, like_ms, like_bytes, like_flops):
+        def frac(ms_, b, f):
+            return round(max(b / hbm, f / peak) / (ms_ * 1e-3), 4)
+        rows.append({"kernel": name, "ms": round(ms, 4), "frac": frac(ms, nbytes, flops), "like": like,
+                     "like_ms": round(like_ms, 4) if like_ms else None,
+                     "like_frac": frac(like_ms, like_bytes, like_flops) if like_ms else None})
+
+    T = tokens
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=dev, dtype=torch.float32).to(dt)
+    # a normed result joins the stream and the next norm reads it
+    x, a = rnd(T, W, dt=torch.float32), rnd(T, W)
+    o1 = torch.empty(T, W, device=dev, dtype=bf)
+    w = [rnd(W, dt=torch.float32) for _ in range(2)]
+    t_v = _median_ms(lambda: K.add_normed_norm(x, a, w[0], 1e-5, w[1], 1e-5, o1), flush=flush)
+    t_h = _median_ms(lambda: K.add_rmsnorm(x, a, w[0], 1e-5, o1), flush=flush)
+    add("add_normed_norm", "add_rmsnorm", t_v, T * W * (4 + 4 + 2 + 2), 0, t_h, T * W * (4 + 4 + 2 + 2), 0)
+    # activations: the routed feed-forward's (erf gelu times routing weight) and the dense one's
+    moe = next(l["mlp"] for l in vcfg["layers"] if l["mlp"]["kind"] == "moe")
+    E, F = moe["router"]["experts"], moe["expert"]["ff"]
+    cols = E * F + moe["shared"]["ff"]
+    up, act = rnd(T, cols), torch.empty(T, cols, device=dev, dtype=bf)
+    route = torch.rand(T, E, device=dev)
+    gu, act_h = rnd(T, 2 * ffh), torch.empty(T, ffh, device=dev, dtype=bf)
+    t_h = _median_ms(lambda: K.silu_mul(gu, act_h, False), flush=flush)
+    t_v = _median_ms(lambda: K.ffn_activation(up, act, "gelu", route, F, E * F), flush=flush)
+    add("ffn_activation (gelu x routing weight)", "silu_mul", t_v, T * cols * 4, 0, t_h, T * ffh * 6, 0)
+    up2, act2 = rnd(T, ffh), torch.empty(T, ffh, device=dev, dtype=bf)
+    t_v = _median_ms(lambda: K.ffn_activation(up2, act2, "relu2"), flush=flush)
+    add("ffn_activation (squared relu)", "silu_mul", t_v, T * ffh * 4, 0, t_h, T * ffh * 6, 0)
+    logits = rnd(T, E, dt=torch.float32)
+    idx, wt = torch.empty(T, 2, dtype=torch.int32, device=dev), torch.empty(T, 2, device=dev)
+    t_v = _median_ms(lambda: K.route_topk(logits, route, idx, wt), flush=flush)
+    add("route_topk", None, t_v, T * E * 8, 0, 0, 0, 0)
+    del up, act, gu, act_h, up2, act2
+    ps = 64
+    for kind, n_req, q_len, kv in (("prefill", 1, T, T), ("decode", batch, 1, context)):
+        blocks = -(-kv // ps)
+        pages = n_req * blocks
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(n_req, blocks)
+        cu = np.arange(n_req + 1, dtype=np.int32) * q_len
+        kvl = np.full(n_req, kv, dtype=np.int32)
+        cu_d, kv_d = torch.from_numpy(cu).to(dev), torch.from_numpy(kvl).to(dev)
+        n = n_req * q_len
+        pos = torch.from_numpy(np.concatenate([np.arange(kv - q_len, kv, dtype=np.int32)] * n_req)).to(dev)
+        ent = torch.from_numpy(np.repeat(np.arange(n_req, dtype=np.int32), q_len)).to(dev)
+        slots = torch.arange(n_req, dtype=torch.int32, device=dev)
+        # the recurrence and what prepares it
+        hd = H * dd
+        pcols = 5 * hd + R
+        proj = rnd(n, pcols)
+        w2, w0, ab, nw = rnd(R, hd), rnd(hd, dt=torch.float32), rnd(hd, dt=torch.float32), rnd(hd, dt=torch.float32)
+        aux = torch.empty(n, 3 * hd, device=dev)
+        state = torch.zeros(n_req, H, dd, dd, device=dev)
+        od = torch.empty(n, hd, device=dev, dtype=bf)
+        t_p = _median_ms(lambda: K.delta_rule_prep(proj, pcols, ent, w2, w0, ab, aux, H, dd, math.exp(-0.5), 1e-6, bf),
+                         flush=flush)
+        K.delta_rule_prep(proj, pcols, ent, w2, w0, ab, aux, H, dd, math.exp(-0.5), 1e-6, bf)
+        t_s = _median_ms(lambda: K.delta_rule_scan(proj, pcols, aux, cu_d, kv_d, slots, state, nw, 1e-5, od, H, dd, err),
+                         flush=flush)
+        # attention of the other model, and this one's (the warp-level kernels with the sink)
+        k_pool, v_pool = rnd(pages, nkv, ps, d), rnd(pages, nkv, ps, d)
+        qh, oh = rnd(n, nq * d), torch.empty(n, nq * d, device=dev, dtype=bf)
+        qkv = rnd(n, (nq + 2 * nkv) * d)
+        qw, kw = rnd(nq * d, dt=torch.float32), rnd(nkv * d, dt=torch.float32)
+        cos = sin = torch.ones(max(kv, 1) + 1, d // 2, device=dev)
+        t_c = _median_ms(lambda: K.projection_norm_cache(qkv, qkv.shape[1], pos, ent, table, ps, qw, kw, 1e-5, qh, k_pool,
+                                                         v_pool, nq, nkv, d, d, err), flush=flush)
+        qn, kn = rnd(d, dt=torch.float32), rnd(d, dt=torch.float32)
+        t_rc = _median_ms(lambda: K.rope_norm_cache(qkv, qkv.shape[1], bf, pos, ent, table, cos, sin, qn, kn, 1e-5, qh,
+                                                    k_pool, v_pool, ps, nq, nkv, d, True, True, err), flush=flush)
+        io = n * (nq + 2 * nkv) * d * 2
+        add(f"projection_norm_cache ({kind})", "rope_norm_cache", t_c, io + n * (nq + 2 * nkv) * d * 2, 0, t_rc,
+            io + n * (nq + 2 * nkv) * d * 2, 0)
+        add(f"delta_rule_prep ({kind})", "rope_norm_cache", t_p, n * (3 * hd + R) * 2 + n * 3 * hd * 4, 0, t_rc,
+            io + n * (nq + 2 * nkv) * d * 2, 0)
+        if kind == "prefill":
+            tiles = -(-T // 128)
+            t_h = _median_ms(lambda: K.prefill_attention_tc(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, tiles, nq,
+                                                            nkv, d, 0, d ** -0.5, err), flush=flush)
+            tiles64 = -(-T // 64)
+            t_w = _median_ms(lambda: K.paged_prefill_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, tiles64,
+                                                               nq, nkv, d, 0, d ** -0.5, err, sink=True), flush=flush)
+            pairs = T * T / 2
+            add("sink attention, prompt (paged_prefill_attn with the sink)", "prefill_attn_tc", t_w, 0, pairs * nq * 4 * d,
+                t_h, 0, pairs * nq * 4 * d)
+            # the recurrence: per token and head 3 d^2 multiply-adds in 32-bit; its roofline is the FP32 rate,
+            # reported here against the bytes it must move (inputs, outputs) as the other kernels are
+            add("delta_rule_scan, prompt", "prefill_attn_tc", t_s, n * (4 * hd * 2 + 3 * hd * 4 + hd * 2), 0,
+                t_h, 0, pairs * nq * 4 * d)
+        else:
+            splits = K.decode_splits(n_req, nkv, 148, 64, max_keys=kv)
+            po = torch.empty(n_req * nq * splits, d, device=dev)
+            pml = torch.empty(n_req * nq * splits, 2, device=dev)
+            t_h = _median_ms(lambda: K.paged_decode_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, nq, nkv,
+                                                              d, 0, d ** -0.5, splits, po, pml, err), flush=flush)
+            t_w = _median_ms(lambda: K.paged_decode_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, nq, nkv,
+                                                              d, 0, d ** -0.5, splits, po, pml, err, sink=True), flush=flush)
+            add("sink attention, decoded tokens (paged_decode_attn with the sink)", "paged_decode_attn", t_w,
+                n_req * kv * nkv * d * 2 * 2, 0, t_h, n_req * kv * nkv * d * 2 * 2, 0)
+            add("delta_rule_scan, decoded tokens", "paged_decode_attn", t_s, n_req * H * dd * dd * 4 * 2, 0,
+                t_h, n_req * kv * nkv * d * 2 * 2, 0)
+        del proj, aux, state, k_pool, v_pool, qkv
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    return rows
+
+
+def vodelix_workload(args, pk):
+    """Prefill and decode throughput of Vodelix at the layer sizes of --sizes beside Hunyuan Dense
+    (the engine's closest model) at the same width, layers and vocabulary, random weights, and the
+    kernels of the two side by side."""
+    import gc
+    import torch
+    hcfg = dict(MODEL)
+    hcfg.update(OTHER_SIZES.get(args.sizes, {}))
+    layers = args.layers or 16
+    hcfg["num_hidden_layers"] = layers
+    hcfg["max_position_embeddings"] = max(hcfg["max_position_embeddings"], args.context + 2048)
+    vcfg = vodelix_config(hcfg, layers)
+    page, pt = 64, args.prefill_tokens
+    out = {"workload": "vodelix", "sizes": args.sizes, "layers": layers, "batch": args.batch,
+           "context": args.context, "prefill_tokens": pt, "dtype": "bf16", "data": "synthetic", "models": {}}
+    for name, cfg, vocab in (("vodelix", vcfg, vcfg["vocab"]), ("hunyuan_dense", hcfg, hcfg["vocab_size"])):
+        opts = dict(page_size=page, num_pages=(args.batch * (args.context + args.steps + args.warmup + 64) + pt) // page + 64,
+                    max_concurrent=max(64, args.batch), max_seq_len=max(args.context, pt) + 1024,
+                    max_batched_tokens=max(2048, pt), chunk_size=max(2048, pt))
+        model = build_model(cfg, opts)
+        pms = time_prefill(model, pt, vocab, reps=3)
+        ids = fill_cache(model, args.batch, args.context)
+        dms, launches = time_decode(model, ids, args.steps, args.warmup, vocab)
+        weights = sum(t.numel() * t.element_size() for t in _model_tensors(model))
+        out["models"][name] = {"prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(pt * 1000.0 / pms, 1),
+                               "decode_ms_per_step": round(dms, 4),
+                               "decode_tokens_per_s": round(args.batch * 1000.0 / dms, 1),
+                               "launches_per_decode_step": launches, "weight_bytes": weights,
+                               "layer_runs": len(model.runner.spec.schedule)}
+        del model
+        gc.collect()
+        torch.cuda.empty_cache()
+    out["kernels"] = vodelix_kernel_table(vcfg, hcfg, pk, pt, args.batch, args.context)
+    out["peaks"] = pk
+    return out
+
+
 def _model_tensors(model):
     seen, out = set(), []
     parts = [model.runner.model.embed, model.runner.model.final_norm, model.runner.model.head]
@@ -644,10 +830,11 @@ def main():
                     help="layer sizes: Hunyuan 1.8B (the default, the headline configuration), 4B or 7B")
     ap.add_argument("--prefill-chunk", type=int, default=0,
                     help="with --only-prefill: also time the prompt in portions of this many tokens, a step each")
-    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step", "radorax"],
+    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step", "radorax", "vodelix"],
                     help="serve: a mix of requests through the scheduler; mixed-step: decoded tokens beside "
                          "one prompt portion in one step; radorax: prefill and decode of Radorax beside Hunyuan "
-                         "Dense at equal layer sizes, and their kernels side by side; each prints its own record only")
+                         "Dense at equal layer sizes, and their kernels side by side; vodelix: the same for Vodelix; "
+                         "each prints its own record only")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--prompt-min", type=int, default=128)
     ap.add_argument("--prompt-max", type=int, default=4096)
@@ -667,6 +854,9 @@ def main():
         return 2
     args.warmup = max(args.warmup, 3)
 
+    if args.workload == "vodelix":
+        print(json.dumps(vodelix_workload(args, peaks())))
+        return 0
     if args.workload == "radorax":
         print(json.dumps(radorax_workload(args, peaks())))
         return 0

@@ -10,8 +10,9 @@
 //    w the decay per key channel, a the removal rate, u the key scaled to unit length; both
 //    corrections read the state before the token.  `delta_rule_prep` forms w, a * u and u of every
 //    token in 32-bit; `delta_rule_scan` walks each request's tokens in order with the state of a head
-//    spread over the threads of a CTA (a thread owns a column of S: columns do not talk to one
-//    another), then norms each head's read-out, gates it and writes it for the output projection.
+//    spread over the threads of a CTA (columns of S do not talk to one another; a column's rows are
+//    spread over a few lanes), then norms each head's read-out, gates it and writes it for the output
+//    projection.
 //    The state lives in 32-bit in the request's slot between steps.
 #include "common.cuh"
 
@@ -76,41 +77,65 @@ projection_norm_cache_kernel(GemmOut<T> qkv, int cols, const int* __restrict__ p
 // the decay's inner product.  aux row (float): [w | a * u | u], each heads * d.
 //   w = exp(-decay_scale * sigmoid(sum_j w2[c][j] tanh(low[j]) + w0[c]))
 //   a = sigmoid(a_pre + ab[c]);  u = k / sqrt(sum over the head of k^2 + key_eps)
-// One CTA per token; a warp per head for the key's length.
+// `w2t` is w2 turned over, [rank][heads * d], so that neighbouring threads (channels) read neighbouring
+// weights.  A CTA takes PREP_TOKENS tokens and a block of whole heads: every weight it reads serves
+// all its tokens.
+constexpr int PREP_TOKENS = 8;
+
 template <typename T>
 __global__ void __launch_bounds__(256)
-delta_rule_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_entry, const T* __restrict__ w2,
+delta_rule_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_entry, const T* __restrict__ w2t,
                        const float* __restrict__ w0, const float* __restrict__ ab, float* __restrict__ aux,
-                       int heads, int d, int rank, float decay_scale, float key_eps) {
-    extern __shared__ float sm[];          // [rank] tanh(low), [heads] 1 / |k|
+                       int n_tokens, int heads, int d, int rank, int heads_per_cta, float decay_scale,
+                       float key_eps) {
+    extern __shared__ float sm[];          // [PREP_TOKENS][rank] tanh(low), [PREP_TOKENS][heads_per_cta] 1 / |k|
     float* th = sm;
-    float* inv_len = sm + rank;
+    float* inv_len = sm + PREP_TOKENS * rank;
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
-    if (tok_entry[t] < 0) return;
+    const int t0 = blockIdx.x * PREP_TOKENS;
+    const int nt = min(PREP_TOKENS, n_tokens - t0);
+    const int h0 = blockIdx.y * heads_per_cta;
+    const int nh = min(heads_per_cta, heads - h0);
     const int hd = heads * d;
-    const long long base = (long long)t * cols;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(proj.load(base + 5 * hd + j));
+    for (int idx = threadIdx.x; idx < PREP_TOKENS * rank; idx += blockDim.x) {
+        const int tt = idx / rank, j = idx % rank;
+        th[idx] = tt < nt ? tanhf(proj.load((long long)(t0 + tt) * cols + 5 * hd + j)) : 0.f;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    for (int h = warp; h < heads; h += nwarps) {
+    for (int idx = warp; idx < nt * nh; idx += nwarps) {
+        const int tt = idx / nh, h = idx % nh;
+        const long long kb = (long long)(t0 + tt) * cols + hd + (h0 + h) * d;
         float ss = 0.f;
-        for (int i = lane; i < d; i += 32) { const float kv = proj.load(base + hd + h * d + i); ss += kv * kv; }
+        for (int i = lane; i < d; i += 32) { const float kv = proj.load(kb + i); ss += kv * kv; }
         ss = warp_sum(ss);
-        if (lane == 0) inv_len[h] = rsqrtf(ss + key_eps);
+        if (lane == 0) inv_len[tt * heads_per_cta + h] = rsqrtf(ss + key_eps);
     }
     __syncthreads();
-    float* out = aux + (long long)t * 3 * hd;
-    for (int c = threadIdx.x; c < hd; c += blockDim.x) {
-        float low = w0[c];
-        const T* wr = w2 + (long long)c * rank;
-        for (int j = 0; j < rank; ++j) low = fmaf(to_f32(wr[j]), th[j], low);
-        const float w = expf(-decay_scale / (1.f + expf(-low)));
-        const float a = 1.f / (1.f + expf(-(proj.load(base + 4 * hd + c) + ab[c])));
-        const float u = proj.load(base + hd + c) * inv_len[c / d];
-        out[c] = w;
-        out[hd + c] = a * u;
-        out[2 * hd + c] = u;
+    for (int cc = threadIdx.x; cc < nh * d; cc += blockDim.x) {
+        const int c = h0 * d + cc;
+        float low[PREP_TOKENS];
+        const float b0 = w0[c];
+#pragma unroll
+        for (int tt = 0; tt < PREP_TOKENS; ++tt) low[tt] = b0;
+        for (int j = 0; j < rank; ++j) {
+            const float wv = to_f32(w2t[(long long)j * hd + c]);
+#pragma unroll
+            for (int tt = 0; tt < PREP_TOKENS; ++tt) low[tt] = fmaf(wv, th[tt * rank + j], low[tt]);
+        }
+        const float bias = ab[c];
+#pragma unroll
+        for (int tt = 0; tt < PREP_TOKENS; ++tt) {
+            if (tt >= nt || tok_entry[t0 + tt] < 0) continue;
+            const long long base = (long long)(t0 + tt) * cols;
+            const float w = expf(-decay_scale / (1.f + expf(-low[tt])));
+            const float a = 1.f / (1.f + expf(-(proj.load(base + 4 * hd + c) + bias)));
+            const float u = proj.load(base + hd + c) * inv_len[tt * heads_per_cta + cc / d];
+            float* out = aux + (long long)(t0 + tt) * 3 * hd;
+            out[c] = w;
+            out[hd + c] = a * u;
+            out[2 * hd + c] = u;
+        }
     }
 }
 
@@ -242,6 +267,143 @@ delta_rule_scan_kernel(GemmOut<T> proj, int cols, const float* __restrict__ aux,
     }
 }
 
+// The same recurrence for heads of at most 128 elements, a column's rows spread over P = 1, 2, 4 or
+// 8 lanes of a warp (at most SPLIT_ROWS rows each, in registers): the chain of multiply-adds per token
+// is SPLIT_ROWS long instead of d, the partial sums of u^T S and of the read-out go round by
+// shuffles, and there is no block barrier inside a tile.  Lane = part * (32 / P) + column in the warp,
+// so neighbouring lanes hold neighbouring columns.  In shared memory every per-token vector over the
+// key channels lies in P segments SPLIT_SEG apart (the rows of a part, zero-filled to SPLIT_ROWS), so
+// that a part reads its rows as four 16-byte words and the parts of a warp hit different banks.
+// SPLIT_ROWS 16 with at most 256 threads serves heads of up to 64, 32 rows and 512 threads up to 128.
+template <typename T, int SPLIT_ROWS, int MAX_THREADS>
+__global__ void __launch_bounds__(MAX_THREADS, 512 / MAX_THREADS)
+delta_rule_scan_split_kernel(GemmOut<T> proj, int cols, const float* __restrict__ aux,
+                             const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                             const int* __restrict__ slots, int n_slots, float* __restrict__ state,
+                             const float* __restrict__ norm_w, float norm_eps, T* __restrict__ out, int heads,
+                             int d, int P, int rows_pp, int* err) {
+    constexpr int SPLIT_SEG = SPLIT_ROWS + 8;
+    extern __shared__ __align__(16) float sm[];
+    const int VS = P * SPLIT_SEG;                         // floats of one vector
+    float* vec = sm;                                      // [TT][5][VS]  r, k, w, a u, u
+    float* val = vec + TT * 5 * VS;                       // [TT][d]  v
+    float* gat = val + TT * d;                            // [TT][d]  gate, before its sigmoid
+    float* o_s = gat + TT * d;                            // [TT][d]
+    pdl_launch_dependents();
+    for (int i = threadIdx.x; i < TT * 5 * VS; i += blockDim.x) vec[i] = 0.f;     // the rows that pad a part stay zero
+    pdl_wait();
+    const int e = blockIdx.x, h = blockIdx.y;
+    const int first = cu_q[e], n = cu_q[e + 1] - first;
+    if (n <= 0) return;                                  // an entry that pads the step: no slot is touched
+    const int slot = slots[e];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_SLOT_RANGE);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int cpw = 32 / P;
+    const int part = lane / cpw, j = warp * cpw + lane % cpw;
+    const bool own = j < d;
+    const int row0 = part * rows_pp;
+    const int hd = heads * d;
+    float* S_g = state + ((long long)slot * heads + h) * d * d;
+    const bool fresh = kv_len[e] - n == 0;               // the request's first tokens: the state starts at zero
+    float S[SPLIT_ROWS];
+#pragma unroll
+    for (int r = 0; r < SPLIT_ROWS; ++r)
+        S[r] = (!fresh && own && r < rows_pp && row0 + r < d) ? S_g[(row0 + r) * d + j] : 0.f;
+    for (int t0 = 0; t0 < n; t0 += TT) {
+        const int nt = min(TT, n - t0);
+        __syncthreads();                                 // the tile before has been read out
+        for (int tt = warp; tt < nt; tt += nwarps) {
+            const long long row = (long long)(first + t0 + tt);
+            const long long pb = row * cols + h * d;
+            const float* ax = aux + row * 3 * hd + h * d;
+            float* v5 = vec + tt * 5 * VS;
+            for (int c = lane; c < d; c += 32) {
+                const int at = (c / rows_pp) * SPLIT_SEG + c % rows_pp;
+                v5[at] = proj.load(pb + c);                       // r
+                v5[VS + at] = proj.load(pb + hd + c);             // k
+                v5[2 * VS + at] = ax[c];                          // w
+                v5[3 * VS + at] = ax[hd + c];                     // a u
+                v5[4 * VS + at] = ax[2 * hd + c];                 // u
+                val[tt * d + c] = proj.load(pb + 2 * hd + c);
+                gat[tt * d + c] = proj.load(pb + 3 * hd + c);
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* base = vec + tt * 5 * VS + part * SPLIT_SEG;
+            const float v = own ? val[tt * d + j] : 0.f;
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+            for (int q4 = 0; q4 < SPLIT_ROWS / 4; ++q4) {
+                const float4 uu = *(const float4*)(base + 4 * VS + 4 * q4);
+                d0 = fmaf(uu.x, S[4 * q4], d0);
+                d1 = fmaf(uu.y, S[4 * q4 + 1], d1);
+                d2 = fmaf(uu.z, S[4 * q4 + 2], d2);
+                d3 = fmaf(uu.w, S[4 * q4 + 3], d3);
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+            for (int o = cpw; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int q4 = 0; q4 < SPLIT_ROWS / 4; ++q4) {
+                const float4 rr = *(const float4*)(base + 4 * q4);
+                const float4 kk = *(const float4*)(base + VS + 4 * q4);
+                const float4 ww = *(const float4*)(base + 2 * VS + 4 * q4);
+                const float4 aa = *(const float4*)(base + 3 * VS + 4 * q4);
+                const int r = 4 * q4;
+                S[r] = fmaf(ww.x, S[r], fmaf(-aa.x, dot, kk.x * v));
+                S[r + 1] = fmaf(ww.y, S[r + 1], fmaf(-aa.y, dot, kk.y * v));
+                S[r + 2] = fmaf(ww.z, S[r + 2], fmaf(-aa.z, dot, kk.z * v));
+                S[r + 3] = fmaf(ww.w, S[r + 3], fmaf(-aa.w, dot, kk.w * v));
+                o0 = fmaf(rr.x, S[r], o0);
+                o1 = fmaf(rr.y, S[r + 1], o1);
+                o2 = fmaf(rr.z, S[r + 2], o2);
+                o3 = fmaf(rr.w, S[r + 3], o3);
+            }
+            float po = (o0 + o1) + (o2 + o3);
+            for (int o = cpw; o < 32; o <<= 1) po += __shfl_xor_sync(0xffffffffu, po, o);
+            if (own && part == 0) o_s[tt * d + j] = po;
+        }
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += nwarps) {
+            float ss = 0.f;
+            for (int c = lane; c < d; c += 32) { const float v = o_s[tt * d + c]; ss += v * v; }
+            ss = warp_sum(ss);
+            const float rs = rsqrtf(ss / (float)d + norm_eps);
+            T* op = out + (long long)(first + t0 + tt) * hd + h * d;
+            for (int c = lane; c < d; c += 32) {
+                const float g = 1.f / (1.f + expf(-gat[tt * d + c]));
+                op[c] = from_f32<T>(o_s[tt * d + c] * rs * norm_w[h * d + c] * g);
+            }
+        }
+    }
+    if (own) {
+#pragma unroll
+        for (int r = 0; r < SPLIT_ROWS; ++r)
+            if (r < rows_pp && row0 + r < d) S_g[(row0 + r) * d + j] = S[r];
+    }
+}
+
+template <typename T, int SPLIT_ROWS, int MAX_THREADS>
+int launch_scan_split(GemmOut<T> proj, int cols, const float* aux, const int* cu_q, const int* kv_len,
+                      const int* slots, int n_slots, float* state, const float* norm_w, float norm_eps, T* out,
+                      int n_entries, int heads, int d, int* err, cudaStream_t st) {
+    constexpr int SPLIT_SEG = SPLIT_ROWS + 8;
+    int P = 1;
+    while (P * SPLIT_ROWS < d) P *= 2;                   // 1, 2 or 4
+    const int rows_pp = (d + P - 1) / P, cpw = 32 / P;
+    const int warps = (d + cpw - 1) / cpw;
+    const size_t smem = (size_t)(TT * 5 * P * SPLIT_SEG + 3 * TT * d) * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(delta_rule_scan_split_kernel<T, SPLIT_ROWS, MAX_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return crane_launch(delta_rule_scan_split_kernel<T, SPLIT_ROWS, MAX_THREADS>, dim3(n_entries, heads), dim3(warps * 32), smem, st, proj,
+                        cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out, heads, d, P, rows_pp,
+                        err);
+}
+
 template <typename T, int DK>
 int launch_scan(GemmOut<T> proj, int cols, const float* aux, const int* cu_q, const int* kv_len, const int* slots,
                 int n_slots, float* state, const float* norm_w, float norm_eps, T* out, int n_entries, int heads,
@@ -260,16 +422,14 @@ template <typename T>
 int scan_dispatch(GemmOut<T> g, int cols, const float* aux, const int* cu_q, const int* kv_len, const int* slots,
                   int n_slots, float* state, const float* norm_w, float norm_eps, T* out, int n_entries, int heads,
                   int d, int* err, cudaStream_t st) {
-#define SCAN(DK) return launch_scan<T, DK>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out, \
-                                           n_entries, heads, d, err, st)
-    switch (d) {
-        case 16: SCAN(16);
-        case 32: SCAN(32);
-        case 64: SCAN(64);
-        case 128: SCAN(128);
-        default: SCAN(0);
-    }
-#undef SCAN
+    if (d <= 64)
+        return launch_scan_split<T, 16, 256>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out,
+                                             n_entries, heads, d, err, st);
+    if (d <= 128)
+        return launch_scan_split<T, 32, 512>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out,
+                                             n_entries, heads, d, err, st);
+    return launch_scan<T, 0>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out, n_entries,
+                             heads, d, err, st);
 }
 
 }  // namespace
@@ -292,16 +452,18 @@ CRANE_API int crane_projection_norm_cache(int dtype, const void* qkv, const floa
 }
 
 CRANE_API int crane_delta_rule_prep(int dtype, const void* proj, const float* proj_parts, int n_parts,
-                                    long long part_stride, int cols, const int* tok_entry, const void* w2,
+                                    long long part_stride, int cols, const int* tok_entry, const void* w2t,
                                     const float* w0, const float* ab, float* aux, int n_tokens, int heads,
                                     int d, int rank, float decay_scale, float key_eps, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    const size_t smem = (size_t)(rank + heads) * sizeof(float);
+    const int hpc = d >= 256 ? 1 : (256 / d < heads ? 256 / d : heads);
+    const size_t smem = (size_t)(PREP_TOKENS * (rank + hpc)) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const dim3 grid((n_tokens + PREP_TOKENS - 1) / PREP_TOKENS, (heads + hpc - 1) / hpc);
     DISPATCH_T(dtype, {
         GemmOut<T> g{(const T*)proj, proj_parts, n_parts, part_stride};
-        return crane_launch(delta_rule_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, st, g, cols, tok_entry,
-                            (const T*)w2, w0, ab, aux, heads, d, rank, decay_scale, key_eps);
+        return crane_launch(delta_rule_prep_kernel<T>, grid, dim3(256), smem, st, g, cols, tok_entry,
+                            (const T*)w2t, w0, ab, aux, n_tokens, heads, d, rank, hpc, decay_scale, key_eps);
     });
 }
 

@@ -75,31 +75,63 @@ __global__ void __launch_bounds__(256)
 add_normed_norm_kernel(float* __restrict__ x, GemmOut<T> delta, const float* __restrict__ wd,
                        const float* __restrict__ wo, T* __restrict__ out, T* __restrict__ raw,
                        int hidden, float eps_d, float eps_o) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const long long base = (long long)blockIdx.x * hidden;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float d = delta.load(base + c);
-        row[c] = d;
-        ss += d * d;
+    // (rows of a multiple of 4 columns go four columns a thread and pass; `hidden` and the tensors'
+    // alignment are the same for every row, so the branch is uniform)
+    const bool quad = hidden % 4 == 0 && delta.parts == nullptr && ((uintptr_t)delta.whole % 8) == 0 &&
+                      ((uintptr_t)x | (uintptr_t)wd | (uintptr_t)wo) % 16 == 0 && ((uintptr_t)out | (uintptr_t)raw) % 8 == 0;
+    if (quad) {
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            const float2 a = ld2(delta.whole + base + c), b = ld2(delta.whole + base + c + 2);
+            *(float4*)(row + c) = make_float4(a.x, a.y, b.x, b.y);
+            ss += (a.x * a.x + a.y * a.y) + (b.x * b.x + b.y * b.y);
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float d = delta.load(base + c);
+            row[c] = d;
+            ss += d * d;
+        }
     }
     ss = block_sum(ss, scratch);
     const float rd = rsqrtf(ss / (float)hidden + eps_d);
     float sx = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = x[base + c] + row[c] * rd * wd[c];
-        x[base + c] = v;
-        row[c] = v;
-        sx += v * v;
-        if (raw != nullptr) raw[base + c] = from_f32<T>(v);
+    if (quad) {
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            const float4 xv = *(const float4*)(x + base + c), dv = *(const float4*)(row + c), wv = *(const float4*)(wd + c);
+            const float4 v = make_float4(xv.x + dv.x * rd * wv.x, xv.y + dv.y * rd * wv.y, xv.z + dv.z * rd * wv.z,
+                                         xv.w + dv.w * rd * wv.w);
+            *(float4*)(x + base + c) = v;
+            *(float4*)(row + c) = v;
+            sx += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+            if (raw != nullptr) { st2(raw + base + c, v.x, v.y); st2(raw + base + c + 2, v.z, v.w); }
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float v = x[base + c] + row[c] * rd * wd[c];
+            x[base + c] = v;
+            row[c] = v;
+            sx += v * v;
+            if (raw != nullptr) raw[base + c] = from_f32<T>(v);
+        }
     }
     if (out == nullptr) return;
     sx = block_sum(sx, scratch);
     const float ro = rsqrtf(sx / (float)hidden + eps_o);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[base + c] = from_f32<T>(row[c] * ro * wo[c]);
+    if (quad) {
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            const float4 v = *(const float4*)(row + c), wv = *(const float4*)(wo + c);
+            st2(out + base + c, v.x * ro * wv.x, v.y * ro * wv.y);
+            st2(out + base + c + 2, v.z * ro * wv.z, v.w * ro * wv.w);
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[base + c] = from_f32<T>(row[c] * ro * wo[c]);
+    }
 }
 
 // ------------------------------------------------------ gate of the per-layer token input
@@ -150,6 +182,44 @@ ffn_activation_kernel(GemmOut<T> up, T* __restrict__ out, long long n, int cols,
         }
         out[i] = from_f32<T>(a);
     }
+}
+
+// The same for bfloat16 rows whose columns come in whole groups of 8: a thread takes 8 neighbouring
+// columns of one row (16 bytes in, 16 bytes out); grid (column groups, rows).
+__global__ void __launch_bounds__(256)
+ffn_activation_vec_kernel(const __nv_bfloat16* __restrict__ up, __nv_bfloat16* __restrict__ out, int cols, int kind,
+                          const float* __restrict__ route, int experts, int per_expert, int routed_cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c0 >= cols) return;
+    const long long row = blockIdx.y;
+    const uint4 raw = *(const uint4*)(up + row * cols + c0);
+    const __nv_bfloat162* in2 = (const __nv_bfloat162*)&raw;
+    float w = 1.f;
+    if (route != nullptr && c0 < routed_cols) w = route[row * experts + c0 / per_expert];
+    uint4 res;
+    __nv_bfloat162* out2 = (__nv_bfloat162*)&res;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 z = __bfloat1622float2(in2[i]);
+        float a[2] = {z.x, z.y};
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float v = a[k];
+            if (kind == 0) {
+                const float r = fmaxf(v, 0.f);
+                a[k] = r * r;
+            } else if (kind == 1) {
+                a[k] = 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+            } else {
+                a[k] = gelu_tanh_f(v);
+            }
+            a[k] = w == 0.f ? 0.f : a[k] * w;
+        }
+        out2[i] = __floats2bfloat162_rn(a[0], a[1]);
+    }
+    *(uint4*)(out + row * cols + c0) = res;
 }
 
 // ------------------------------------------------------ router
@@ -252,6 +322,11 @@ CRANE_API int crane_ffn_activation(int dtype, const void* up, const float* up_pa
     if (n_rows <= 0 || cols <= 0) return 0;
     const long long n = (long long)n_rows * cols;
     const int blocks = (int)((n + 1023) / 1024 < 8192 ? (n + 1023) / 1024 : 8192);
+    if (dtype == 1 && up != nullptr && cols % 8 == 0 && n_rows <= 65535 && ((uintptr_t)up | (uintptr_t)out) % 16 == 0 &&
+        (route == nullptr || (per_expert % 8 == 0 && routed_cols % 8 == 0)))
+        return crane_launch(ffn_activation_vec_kernel, dim3((cols / 8 + 255) / 256, n_rows), dim3(256), 0, st,
+                            (const __nv_bfloat16*)up, (__nv_bfloat16*)out, cols, kind, route, experts, per_expert,
+                            routed_cols);
     DISPATCH_T(dtype, {
         GemmOut<T> u{(const T*)up, up_parts, n_parts, part_stride};
         return crane_launch(ffn_activation_kernel<T>, dim3(blocks), dim3(256), 0, st, u, (T*)out, n, cols, kind,

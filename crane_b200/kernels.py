@@ -354,14 +354,15 @@ class Kernels:
         self.lib.crane_delta_rule_max_dim.restype = c_int
         return int(self.lib.crane_delta_rule_max_dim())
 
-    def delta_rule_prep(self, proj: Act, cols, tok_entry, w2, w0, ab, aux, heads, d, decay_scale, key_eps,
+    def delta_rule_prep(self, proj: Act, cols, tok_entry, w2t, w0, ab, aux, heads, d, decay_scale, key_eps,
                         dtype) -> None:
         """aux [n, 3, heads d] (float) = decay, removal rate x unit key, unit key of every token, from
-        rows [r | k | v | g | a | low (rank)] of the merged projection."""
+        rows [r | k | v | g | a | low (rank)] of the merged projection.  ``w2t`` [rank, heads d]: the
+        decay's second matrix turned over."""
         whole, parts, n_parts, stride = _split(proj)
         self._check(self.lib.crane_delta_rule_prep(
-            _dt(dtype), whole, parts, n_parts, stride, int(cols), tok_entry.data_ptr(), w2.data_ptr(), w0.data_ptr(),
-            ab.data_ptr(), aux.data_ptr(), aux.shape[0], heads, d, w2.shape[1], float(decay_scale), float(key_eps),
+            _dt(dtype), whole, parts, n_parts, stride, int(cols), tok_entry.data_ptr(), w2t.data_ptr(), w0.data_ptr(),
+            ab.data_ptr(), aux.data_ptr(), aux.shape[0], heads, d, w2t.shape[0], float(decay_scale), float(key_eps),
             self._stream(aux)), "delta_rule_prep")
 
     def delta_rule_scan(self, proj: Act, cols, aux, cu_q, kv_len, slots, state, norm_w, norm_eps, out, heads, d,

@@ -67,10 +67,10 @@ class GeneralDelta(Part):
         # one product for everything that reads the block's input: [r | k | v | g | a | w1]
         self.w_in = torch.cat([weights.pop(p + nm[n]) for n in ("r", "k", "v", "g", "a", "w1")], dim=0).contiguous()
         self.cols = self.w_in.shape[0]
-        self.w2 = weights[p + nm["w2"]]
+        self.w2t = weights.pop(p + nm["w2"]).t().contiguous()         # [rank, H dim]: channels side by side
         self.w0, self.a_bias, self.norm_w = weights[p + nm["w0"]], weights[p + nm["a_bias"]], weights[p + nm["norm"]]
         self.o_w = weights[p + nm["o"]]
-        if self.w2.shape[1] != self.cols - 5 * self.H * self.d:
+        if self.w2t.shape[0] != self.cols - 5 * self.H * self.d:
             raise ValueError(f"{p}: the decay's two matrices do not share their inner size")
 
     def cache_need(self) -> CacheNeed:
@@ -82,7 +82,7 @@ class GeneralDelta(Part):
         hd = self.H * self.d
         proj = rt.linear(h, self.w_in, None, "delta_proj")
         aux = rt.ws.get("delta_aux", n, 3 * hd, torch.float32)
-        k.delta_rule_prep(proj, self.cols, ctx.tok_entry, self.w2, self.w0, self.a_bias, aux, self.H, self.d,
+        k.delta_rule_prep(proj, self.cols, ctx.tok_entry, self.w2t, self.w0, self.a_bias, aux, self.H, self.d,
                           self.decay_scale, self.key_eps, rt.dtype)
         o = rt.ws.get("delta_o", n, hd, rt.dtype)
         k.delta_rule_scan(proj, self.cols, aux, ctx.cu_q, ctx.kv_len, ctx.slots, cache.state, self.norm_w,

@@ -42,9 +42,11 @@ def cases(model_folders):
 # logits are compared in the bulk: the median error and the share of positions within the bound.  The
 # sharp checks of cache, state and batching are the 32-bit runs, which take the same way through the
 # host's code, and the kernels' own tests, which run both types.
-def _compare(got, tb, plain, dtype, label, tol_rms=None):
-    if dtype == "float32" and tol_rms is None:
-        return tt.compare(got, tb, plain, dtype, label)
+def _compare(got, tb, plain, dtype, label, tol_rms=3e-5):
+    """(32-bit: every row's root-mean-square error relative to the row's own.  Layers that norm what
+    they add carry a stream of 30 to 80 in size, whose roundings the final norm scales with it: the
+    engine's 32-bit logits sit 2e-6 to 1.5e-5 from the 64-bit ones, where a wrong key or a lost state
+    shows as 1e-2 and more.)"""
     errs = []
     for sid in sorted(tb.rows):
         want = tt.expected_rows(tb.rows[sid], plain)
@@ -72,7 +74,9 @@ def test_alone_whole_tail_portions(name, dtype, cases, tmp_path):
     got = tt.run_trace(folder, dtype, tb.steps, tb.peak_tokens, ps, str(tmp_path / "out"))
     _compare(got, tb, plain, dtype, f"config {name}")
     if dtype == "float32":
-        tt.compare_cuts([(got, tb)], dtype, f"config {name}")
+        # (the norm kernels for few and for many rows add in different orders: cuttings agree to
+        # rounding, not to the bit, and the stream's size scales that as it scales the error above)
+        tt.compare_cuts([(got, tb)], dtype, f"config {name}", tol=3e-5)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -368,7 +372,8 @@ def _plain_delta(proj, H, d, R, w2, w0, ab, norm_w, eps, state):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H, d, R", [(3, 16, 4), (2, 32, 8), (1, 64, 16), (2, 128, 8), (3, 24, 5), (2, 48, 12), (1, 136, 3)])
+@pytest.mark.parametrize("H, d, R", [(3, 16, 4), (2, 32, 8), (1, 64, 16), (2, 128, 8), (3, 24, 5), (2, 48, 12), (1, 136, 3),
+                                     (5, 18, 7), (2, 100, 9), (1, 8, 2), (9, 64, 64)])
 def test_delta_rule_kernels(K, dtype, H, d, R):
     """Three steps over four slots: prompts of unequal length, their continuation (one of them a
     single token) beside a new request in a slot that was used before, with rows and entries
@@ -378,8 +383,8 @@ def test_delta_rule_kernels(K, dtype, H, d, R):
     w2, w0, ab = rng.standard_normal((hd, R)) * 0.5, rng.standard_normal(hd), rng.standard_normal(hd)
     norm_w = 1 + 0.2 * rng.standard_normal(hd)
     store = dtype
-    w2_d = _dev(w2, store)
-    w2r = w2_d.double().cpu().numpy()
+    w2_d = _dev(w2.T.copy(), store)                                # the kernel takes it turned over: [rank, heads d]
+    w2r = w2_d.double().cpu().numpy().T
     state = torch.full((4, H, d, d), 9.0, device=DEV)              # what an earlier request left behind
     err = _err()
     tol = 5e-5 if dtype == torch.float32 else 3e-2
