@@ -71,7 +71,7 @@ stream_enter_kernel(float* __restrict__ x, const float* __restrict__ kept, const
 // raw = x in T (if raw).  The weights are what the norms multiply by (an offset is folded in by the host).
 // One CTA per row; the row lives in shared memory between the passes.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 add_normed_norm_kernel(float* __restrict__ x, GemmOut<T> delta, const float* __restrict__ wd,
                        const float* __restrict__ wo, T* __restrict__ out, T* __restrict__ raw,
                        int hidden, float eps_d, float eps_o) {
@@ -92,6 +92,7 @@ add_normed_norm_kernel(float* __restrict__ x, GemmOut<T> delta, const float* __r
             ss += (a.x * a.x + a.y * a.y) + (b.x * b.x + b.y * b.y);
         }
     } else {
+#pragma unroll 4
         for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
             const float d = delta.load(base + c);
             row[c] = d;
@@ -112,6 +113,7 @@ add_normed_norm_kernel(float* __restrict__ x, GemmOut<T> delta, const float* __r
             if (raw != nullptr) { st2(raw + base + c, v.x, v.y); st2(raw + base + c + 2, v.z, v.w); }
         }
     } else {
+#pragma unroll 4
         for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
             const float v = x[base + c] + row[c] * rd * wd[c];
             x[base + c] = v;
@@ -298,7 +300,10 @@ CRANE_API int crane_add_normed_norm(int dtype, float* x, const void* delta, cons
         GemmOut<T> d{(const T*)delta, delta_parts, n_parts, part_stride};
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_normed_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return crane_launch(add_normed_norm_kernel<T>, dim3(n_rows), dim3(256), smem, st, x, d, wd, wo, (T*)out,
+        // few rows (a step of single tokens): more threads a row, so that a thread's loads, each of which
+        // waits for memory, are few
+        const int threads = n_rows <= 64 ? (hidden >= 4096 ? 1024 : hidden >= 1024 ? 512 : 256) : 256;
+        return crane_launch(add_normed_norm_kernel<T>, dim3(n_rows), dim3(threads), smem, st, x, d, wd, wo, (T*)out,
                             (T*)raw, hidden, eps_d, eps_o);
     });
 }

@@ -374,8 +374,8 @@ class Kernels:
         self._check(self.lib.crane_delta_rule_scan(
             _dt(out.dtype), whole, parts, n_parts, stride, int(cols), aux.data_ptr(), cu_q.data_ptr(),
             kv_len.data_ptr(), slots.data_ptr(), state.shape[0], state.data_ptr(), norm_w.data_ptr(),
-            float(norm_eps), out.data_ptr(), kv_len.shape[0], heads, d, err.data_ptr(), self._stream(out)),
-            "delta_rule_scan")
+            float(norm_eps), out.data_ptr(), kv_len.shape[0], heads, d, err.data_ptr(),
+            self._stream(out)), "delta_rule_scan")
 
     # ---- matrix product on the FP32 cores ------------------------------
     def gemm_simt(self, a, w, bias, out) -> None:
