@@ -704,8 +704,9 @@ def vodelix_kernel_table(vcfg, hcfg, pk, tokens, batch, context):
         t_p = _median_ms(lambda: K.delta_rule_prep(proj, pcols, ent, w2, w0, ab, aux, H, dd, math.exp(-0.5), 1e-6, bf),
                          flush=flush)
         K.delta_rule_prep(proj, pcols, ent, w2, w0, ab, aux, H, dd, math.exp(-0.5), 1e-6, bf)
-        t_s = _median_ms(lambda: K.delta_rule_scan(proj, pcols, aux, cu_d, kv_d, slots, state, nw, 1e-5, od, H, dd, err),
-                         flush=flush)
+        o_raw = torch.empty(n, hd, device=dev) if kind == "prefill" else None      # a prompt alone: four CTAs a head
+        t_s = _median_ms(lambda: K.delta_rule_scan(proj, pcols, aux, cu_d, kv_d, slots, state, nw, 1e-5, od, H, dd, err,
+                                                   col_blocks=4, o_raw=o_raw, tok_entry=ent), flush=flush)
         # attention of the other model, and this one's (the warp-level kernels with the sink)
         k_pool, v_pool = rnd(pages, nkv, ps, d), rnd(pages, nkv, ps, d)
         qh, oh = rnd(n, nq * d), torch.empty(n, nq * d, device=dev, dtype=bf)

@@ -293,8 +293,11 @@ __global__ void __launch_bounds__(MAX_THREADS, MIN_CTAS)
 delta_rule_scan_split_kernel(GemmOut<T> proj, int cols, const float* __restrict__ aux,
                              const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                              const int* __restrict__ slots, int n_slots, float* __restrict__ state,
-                             const float* __restrict__ norm_w, float norm_eps, T* __restrict__ out, int heads,
-                             int d, int P, int rows_pp, int* err) {
+                             const float* __restrict__ norm_w, float norm_eps, T* __restrict__ out,
+                             float* __restrict__ o_raw, int heads, int d, int P, int rows_pp, int* err) {
+    // gridDim.z > 1: a head's columns are cut into that many blocks, a CTA each (columns do not talk to one
+    // another, so a long prompt's heads spread over more SMs); the read-out then goes unnormed to `o_raw`
+    // [rows, heads * d] (float), and `delta_rule_finish` norms and gates it.
     constexpr int SEG = SPLIT_ROWS + 8;
     extern __shared__ __align__(16) float sm[];
     const int VS = P * SEG;                               // floats of one vector
@@ -317,7 +320,8 @@ delta_rule_scan_split_kernel(GemmOut<T> proj, int cols, const float* __restrict_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int cpw = 32 / P;
     const int part = lane / cpw;
-    const int j0 = warp * COLS * cpw + lane % cpw;       // column c of this lane is j0 + c * cpw
+    const int col_end = (d / (int)gridDim.z) * ((int)blockIdx.z + 1);                // (d is a multiple of gridDim.z)
+    const int j0 = (d / (int)gridDim.z) * (int)blockIdx.z + warp * COLS * cpw + lane % cpw;   // column c of this lane is j0 + c * cpw
     const int row0 = part * rows_pp;
     const int hd = heads * d;
     float* S_g = state + ((long long)slot * heads + h) * d * d;
@@ -327,7 +331,7 @@ delta_rule_scan_split_kernel(GemmOut<T> proj, int cols, const float* __restrict_
     for (int c = 0; c < COLS; ++c)
 #pragma unroll
         for (int r = 0; r < SPLIT_ROWS; ++r)
-            S[c][r] = (!fresh && j0 + c * cpw < d && r < rows_pp && row0 + r < d) ? S_g[(row0 + r) * d + j0 + c * cpw] : 0.f;
+            S[c][r] = (!fresh && j0 + c * cpw < col_end && r < rows_pp && row0 + r < d) ? S_g[(row0 + r) * d + j0 + c * cpw] : 0.f;
     for (int t0 = 0; t0 < n; t0 += TT) {
         const int nt = min(TT, n - t0);
         __syncthreads();                                 // the tile before has been read out
@@ -387,7 +391,7 @@ delta_rule_scan_split_kernel(GemmOut<T> proj, int cols, const float* __restrict_
             float v[COLS], dot[COLS], po[COLS];
 #pragma unroll
             for (int c = 0; c < COLS; ++c) {
-                v[c] = j0 + c * cpw < d ? val[tt * d + j0 + c * cpw] : 0.f;
+                v[c] = j0 + c * cpw < col_end ? val[tt * d + j0 + c * cpw] : 0.f;
                 dot[c] = 0.f;
                 po[c] = 0.f;
             }
@@ -423,10 +427,14 @@ delta_rule_scan_split_kernel(GemmOut<T> proj, int cols, const float* __restrict_
             if (part == 0) {
 #pragma unroll
                 for (int c = 0; c < COLS; ++c)
-                    if (j0 + c * cpw < d) o_s[tt * d + j0 + c * cpw] = po[c];
+                    if (j0 + c * cpw < col_end) {
+                        if (o_raw != nullptr) o_raw[(long long)(first + t0 + tt) * hd + h * d + j0 + c * cpw] = po[c];
+                        else o_s[tt * d + j0 + c * cpw] = po[c];
+                    }
             }
         }
         __syncthreads();
+        if (o_raw != nullptr) continue;
         for (int tt = warp; tt < nt; tt += nwarps) {
             float ss = 0.f;
             for (int c = lane; c < d; c += 32) { const float x = o_s[tt * d + c]; ss += x * x; }
@@ -443,23 +451,50 @@ delta_rule_scan_split_kernel(GemmOut<T> proj, int cols, const float* __restrict_
     for (int c = 0; c < COLS; ++c)
 #pragma unroll
         for (int r = 0; r < SPLIT_ROWS; ++r)
-            if (j0 + c * cpw < d && r < rows_pp && row0 + r < d) S_g[(row0 + r) * d + j0 + c * cpw] = S[c][r];
+            if (j0 + c * cpw < col_end && r < rows_pp && row0 + r < d) S_g[(row0 + r) * d + j0 + c * cpw] = S[c][r];
 }
 
 template <typename T, int SPLIT_ROWS, int COLS, int MAX_THREADS, int MIN_CTAS>
 int launch_scan_split(GemmOut<T> proj, int cols, const float* aux, const int* cu_q, const int* kv_len,
                       const int* slots, int n_slots, float* state, const float* norm_w, float norm_eps, T* out,
-                      int n_entries, int heads, int d, int* err, cudaStream_t st) {
+                      float* o_raw, int col_blocks, int n_entries, int heads, int d, int* err, cudaStream_t st) {
     constexpr int SEG = SPLIT_ROWS + 8;
     int P = 1;
-    while (P * SPLIT_ROWS < d) P *= 2;                   // 1, 2 or 4
+    while (P * SPLIT_ROWS < d) P *= 2;                   // 1, 2 or 4 (up to 16 with 4 rows a lane)
     const int rows_pp = (d + P - 1) / P, cpw = 32 / P;
-    const int warps = (d + COLS * cpw - 1) / (COLS * cpw);
+    const int warps = (d / col_blocks + COLS * cpw - 1) / (COLS * cpw);
     const size_t smem = (size_t)(TT * 5 * P * SEG + 3 * TT * d) * sizeof(float);
     auto kern = delta_rule_scan_split_kernel<T, SPLIT_ROWS, COLS, MAX_THREADS, MIN_CTAS>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return crane_launch(kern, dim3(n_entries, heads), dim3(warps * 32), smem, st, proj, cols, aux, cu_q, kv_len,
-                        slots, n_slots, state, norm_w, norm_eps, out, heads, d, P, rows_pp, err);
+    return crane_launch(kern, dim3(n_entries, heads, col_blocks), dim3(warps * 32), smem, st, proj, cols, aux, cu_q,
+                        kv_len, slots, n_slots, state, norm_w, norm_eps, out, col_blocks > 1 ? o_raw : nullptr, heads, d,
+                        P, rows_pp, err);
+}
+
+// out = o_raw / rms over the head * norm_w * sigmoid(gate): a warp per (row, head); the gate is column
+// block 3 of the row's merged product.  Rows of no entry are skipped.
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_rule_finish_kernel(const float* __restrict__ o_raw, GemmOut<T> proj, int cols, const int* __restrict__ tok_entry,
+                         const float* __restrict__ norm_w, float norm_eps, T* __restrict__ out, int n_rows, int heads,
+                         int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)n_rows * heads) return;
+    const int t = (int)(w / heads), h = (int)(w % heads);
+    if (tok_entry[t] < 0) return;
+    const int hd = heads * d;
+    const float* o = o_raw + (long long)t * hd + h * d;
+    float ss = 0.f;
+    for (int c = lane; c < d; c += 32) ss += o[c] * o[c];
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / (float)d + norm_eps);
+    for (int c = lane; c < d; c += 32) {
+        const float g = 1.f / (1.f + expf(-proj.load((long long)t * cols + 3 * hd + h * d + c)));
+        out[(long long)t * hd + h * d + c] = from_f32<T>(o[c] * rs * norm_w[h * d + c] * g);
+    }
 }
 
 template <typename T, int DK>
@@ -478,16 +513,30 @@ int launch_scan(GemmOut<T> proj, int cols, const float* aux, const int* cu_q, co
 
 template <typename T>
 int scan_dispatch(GemmOut<T> g, int cols, const float* aux, const int* cu_q, const int* kv_len, const int* slots,
-                  int n_slots, float* state, const float* norm_w, float norm_eps, T* out, int n_entries, int heads,
-                  int d, int* err, cudaStream_t st) {
-#define SPLIT(ROWS, COLS, THREADS, CTAS)                                                                           \
+                  int n_slots, float* state, const float* norm_w, float norm_eps, T* out, float* o_raw,
+                  const int* tok_entry, int n_rows, int col_blocks, int n_entries, int heads, int d, int* err,
+                  cudaStream_t st) {
+#define SPLIT(ROWS, COLS, THREADS, CTAS, BLOCKS)                                                                   \
     return launch_scan_split<T, ROWS, COLS, THREADS, CTAS>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, \
-                                                          norm_eps, out, n_entries, heads, d, err, st)
-    if (d <= 32) SPLIT(16, 1, 64, 8);
-    // (measured on one prompt of 2,048 tokens, 32 heads of 64: 8 or 4 rows a lane, two or four columns a lane
-    // and further warps that fetch the next tile while this one runs all took as long or longer)
-    if (d <= 64) SPLIT(16, 1, 256, 2);
-    if (d <= 128) SPLIT(32, 2, 256, 1);
+                                                          norm_eps, out, o_raw, BLOCKS, n_entries, heads, d, err, st)
+    int lanes4 = 1;                                      // lanes a column takes with 4 rows a lane
+    while (lanes4 * 4 < d) lanes4 *= 2;
+    const bool fits = lanes4 <= 32 && (d / (col_blocks > 0 ? col_blocks : 1) + 32 / lanes4 - 1) / (32 / lanes4) <= 8;
+    if (col_blocks > 1 && o_raw != nullptr && d <= 64 && d % col_blocks == 0 && fits) {
+        // Few, long entries: a head's columns over `col_blocks` CTAs with 4 rows of a column a lane (the chain of
+        // instructions per token is the shortest that way, and the CTAs are small enough to share an SM's
+        // schedulers with little waiting), then the norm and the gate in a kernel of their own.
+        const int rc = [&]() -> int { SPLIT(4, 1, 256, 2, col_blocks); }();
+        if (rc != 0) return rc;
+        const long long warps = (long long)n_rows * heads;
+        return crane_launch(delta_rule_finish_kernel<T>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, st,
+                            (const float*)o_raw, g, cols, tok_entry, norm_w, norm_eps, out, n_rows, heads, d);
+    }
+    if (d <= 32) SPLIT(16, 1, 64, 8, 1);
+    // (measured on one prompt of 2,048 tokens, 32 heads of 64, a CTA a head: 8 or 4 rows a lane, two or four
+    // columns a lane and further warps that fetch the next tile while this one runs all took as long or longer)
+    if (d <= 64) SPLIT(16, 1, 256, 2, 1);
+    if (d <= 128) SPLIT(32, 2, 256, 1, 1);
 #undef SPLIT
     return launch_scan<T, 0>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, out, n_entries,
                              heads, d, err, st);
@@ -542,13 +591,14 @@ CRANE_API int crane_delta_rule_max_dim() {
 CRANE_API int crane_delta_rule_scan(int dtype, const void* proj, const float* proj_parts, int n_parts,
                                     long long part_stride, int cols, const float* aux, const int* cu_q,
                                     const int* kv_len, const int* slots, int n_slots, float* state,
-                                    const float* norm_w, float norm_eps, void* out, int n_entries, int heads,
+                                    const float* norm_w, float norm_eps, void* out, float* o_raw,
+                                    const int* tok_entry, int n_rows, int col_blocks, int n_entries, int heads,
                                     int d, int* err, cudaStream_t st) {
     if (n_entries <= 0) return 0;
     if (d <= 0 || d > 1024) return (int)cudaErrorInvalidValue;
     DISPATCH_T(dtype, {
         GemmOut<T> g{(const T*)proj, proj_parts, n_parts, part_stride};
-        return scan_dispatch<T>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, (T*)out,
-                                n_entries, heads, d, err, st);
+        return scan_dispatch<T>(g, cols, aux, cu_q, kv_len, slots, n_slots, state, norm_w, norm_eps, (T*)out, o_raw,
+                                tok_entry, n_rows, col_blocks, n_entries, heads, d, err, st);
     });
 }

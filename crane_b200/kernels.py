@@ -52,7 +52,7 @@ _SIGNATURES = {
     "crane_route_topk": [P, P, P, P, I, I, I, P],
     "crane_projection_norm_cache": [I, P, P, I, L, I, P, P, P, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I, P, P],
     "crane_delta_rule_prep": [I, P, P, I, L, I, P, P, P, P, P, I, I, I, I, F, F, P],
-    "crane_delta_rule_scan": [I, P, P, I, L, I, P, P, P, P, I, P, P, F, P, I, I, I, P, P],
+    "crane_delta_rule_scan": [I, P, P, I, L, I, P, P, P, P, I, P, P, F, P, P, P, I, I, I, I, I, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -366,16 +366,20 @@ class Kernels:
             self._stream(aux)), "delta_rule_prep")
 
     def delta_rule_scan(self, proj: Act, cols, aux, cu_q, kv_len, slots, state, norm_w, norm_eps, out, heads, d,
-                        err) -> None:
+                        err, col_blocks: int = 1, o_raw=None, tok_entry=None) -> None:
         """The recurrence over every entry's tokens, from and to ``state`` [slots, heads, d, d] (float;
         an entry whose tokens open its request starts from zero), with the head norm and the gate:
-        ``out`` [n, heads d] in the model dtype."""
+        ``out`` [n, heads d] in the model dtype.  ``col_blocks`` > 1 (with ``o_raw`` float [n, heads d]
+        and ``tok_entry``): for few, long entries a head's columns are cut into that many blocks, a CTA
+        each, and a second kernel norms and gates; the kernel falls back to one CTA a head where the
+        head size does not allow it."""
         whole, parts, n_parts, stride = _split(proj)
         self._check(self.lib.crane_delta_rule_scan(
             _dt(out.dtype), whole, parts, n_parts, stride, int(cols), aux.data_ptr(), cu_q.data_ptr(),
             kv_len.data_ptr(), slots.data_ptr(), state.shape[0], state.data_ptr(), norm_w.data_ptr(),
-            float(norm_eps), out.data_ptr(), kv_len.shape[0], heads, d, err.data_ptr(),
-            self._stream(out)), "delta_rule_scan")
+            float(norm_eps), out.data_ptr(), _ptr(o_raw), _ptr(tok_entry), out.shape[0],
+            int(col_blocks) if o_raw is not None and tok_entry is not None else 1, kv_len.shape[0], heads, d,
+            err.data_ptr(), self._stream(out)), "delta_rule_scan")
 
     # ---- matrix product on the FP32 cores ------------------------------
     def gemm_simt(self, a, w, bias, out) -> None:

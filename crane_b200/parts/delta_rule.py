@@ -85,7 +85,12 @@ class GeneralDelta(Part):
         k.delta_rule_prep(proj, self.cols, ctx.tok_entry, self.w2t, self.w0, self.a_bias, aux, self.H, self.d,
                           self.decay_scale, self.key_eps, rt.dtype)
         o = rt.ws.get("delta_o", n, hd, rt.dtype)
+        # Few and long entries (a prompt alone): a head's columns go over four CTAs, or the one CTA per
+        # (entry, head) leaves most of the device idle while it walks the tokens.  (Rows and entries are
+        # part of a padded step's shape, so a recorded graph holds the choice.)
+        blocks = 4 if n >= 64 * ctx.n_entries and 4 * ctx.n_entries * self.H <= 3 * rt.num_sms else 1
+        o_raw = rt.ws.get("delta_o_raw", n, hd, torch.float32) if blocks > 1 else None
         k.delta_rule_scan(proj, self.cols, aux, ctx.cu_q, ctx.kv_len, ctx.slots, cache.state, self.norm_w,
-                          self.eps, o, self.H, self.d, rt.err)
-        rt.launches += 2
+                          self.eps, o, self.H, self.d, rt.err, col_blocks=blocks, o_raw=o_raw, tok_entry=ctx.tok_entry)
+        rt.launches += 2 if blocks == 1 else 3
         return rt.linear(o, self.o_w, None, "delta_out")

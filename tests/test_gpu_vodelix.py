@@ -371,13 +371,14 @@ def _plain_delta(proj, H, d, R, w2, w0, ab, norm_w, eps, state):
     return pv.unit_rms(o, eps).reshape(n, hd) * norm_w * pv.sigmoid(g.reshape(n, hd)), S
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype, blocks", [(torch.float32, 1), (torch.bfloat16, 1), (torch.float32, 4), (torch.bfloat16, 2)])
 @pytest.mark.parametrize("H, d, R", [(3, 16, 4), (2, 32, 8), (1, 64, 16), (2, 128, 8), (3, 24, 5), (2, 48, 12), (1, 136, 3),
                                      (5, 18, 7), (2, 100, 9), (1, 8, 2), (9, 64, 64)])
-def test_delta_rule_kernels(K, dtype, H, d, R):
+def test_delta_rule_kernels(K, dtype, blocks, H, d, R):
     """Three steps over four slots: prompts of unequal length, their continuation (one of them a
     single token) beside a new request in a slot that was used before, with rows and entries
-    that pad the step."""
+    that pad the step.  ``blocks`` > 1: a head's columns over that many CTAs and the norm in a
+    second kernel (where the head size allows it; else the kernel takes one CTA a head by itself)."""
     rng = np.random.default_rng(H * 1000 + d)
     hd, cols = H * d, 5 * H * d + R
     w2, w0, ab = rng.standard_normal((hd, R)) * 0.5, rng.standard_normal(hd), rng.standard_normal(hd)
@@ -408,7 +409,9 @@ def test_delta_rule_kernels(K, dtype, H, d, R):
         K.delta_rule_prep(proj_d, cols, _dev(ent, torch.int32), w2_d, _dev(w0), _dev(ab), aux, H, d, math.exp(-0.5),
                           1e-6, store)
         K.delta_rule_scan(proj_d, cols, aux, _dev(cu, torch.int32), _dev(kv, torch.int32), _dev(slots, torch.int32),
-                          state, _dev(norm_w), 1e-5, out, H, d, err)
+                          state, _dev(norm_w), 1e-5, out, H, d, err, col_blocks=blocks,
+                          o_raw=torch.zeros(n_rows, hd, device=DEV) if blocks > 1 else None,
+                          tok_entry=_dev(ent, torch.int32))
         got = out.double().cpu().numpy()
         for e, (r, s, n) in enumerate(entries):
             before = plain_state.get(r, np.zeros((H, d, d)))
